@@ -10,7 +10,9 @@ groups of layers with different needs, and slots for per-request state of fixed 
 * **Groups** are formed by what the layers need: all earlier keys (window None) or
   the last W positions.  A windowed group gives pages back as soon as every
   position in them has fallen out of the window of the request's next query; the
-  group of full layers keeps them until the request ends.
+  group of full layers keeps them until the request ends.  A window that also keeps
+  the first F positions of a request readable forms a group of its own (key
+  ``(W, F)``) that never gives back the pages holding those positions.
 * A request holds a **slot**: the row of its block tables and the index of its
   state in every :class:`StateSpec` tensor ([max_slots, *shape], zeroed at
   admission).  Freed pages and slots are used again, most recently freed first.
@@ -54,6 +56,7 @@ class LayerCache:
     state: Optional[torch.Tensor]  # [max_slots, *shape]
     writes: bool = True
     window: Optional[int] = None
+    keep_first: int = 0
     states: Optional[Dict[str, torch.Tensor]] = None  # a state made of named tensors, each [max_slots, *shape]
     table_host: Optional[np.ndarray] = None  # the host's view of the block table (int32 [max_slots, table_width]), for
     #                                          mixers that plan a prompt step's work from the pages it reads
@@ -89,9 +92,10 @@ class _PoolView:
 
 
 class _Group:
-    def __init__(self, mgr, index, window, n_pages, max_slots, width, device):
+    def __init__(self, mgr, index, window, n_pages, max_slots, width, device, keep_first=0):
         self.index = index
         self.window = window
+        self.keep_first = keep_first
         self.caches: List[int] = []
         self.pool = _PoolView(mgr, index, n_pages)
         self.table_dev = torch.full((max_slots, width), -1, dtype=torch.int32, device=device)
@@ -140,10 +144,13 @@ class CacheManager:
             st = None
             pages: Dict[str, torch.Tensor] = {}
             if cs is not None and cs.paged is not None:
-                key = cs.paged.window
+                window = cs.paged.window
+                keep = int(getattr(cs.paged, "keep_first", 0) or 0) if window is not None else 0
+                key = window if keep == 0 else (window, keep)
                 if key not in self.groups:
                     n = n_pages[key] if isinstance(n_pages, dict) else int(n_pages)
-                    self.groups[key] = _Group(self, len(self.groups), key, n, self.max_slots, self.table_width, self.device)
+                    self.groups[key] = _Group(self, len(self.groups), window, n, self.max_slots, self.table_width,
+                                              self.device, keep_first=keep)
                 g = self.groups[key]
                 g.caches.append(idx)
                 for ts in cs.paged.tensors:
@@ -171,6 +178,9 @@ class CacheManager:
                                             self.max_positions)
         if not self._h:
             raise CacheError("the native cache object could not be made")
+        for g in order:
+            if g.keep_first:
+                self._lib.fxh_set_keep_first(self._h, g.index, g.keep_first)
         for g in order:
             g.table = np.ctypeslib.as_array(self._lib.fxh_table(self._h, g.index), shape=(self.max_slots, self.table_width))
         self._order = order
@@ -222,7 +232,7 @@ class CacheManager:
     def pages_needed(self, slot: int, new_len: int) -> Dict[object, int]:
         """Pages each group still has to get so that positions < new_len are mapped."""
         self._ok(self._lib.fxh_pages_needed(self._h, int(slot), int(new_len), self._need), slot)
-        return {g.window: self._need[g.index] for g in self._order}
+        return {self._key(g): self._need[g.index] for g in self._order}
 
     def free_pages(self) -> Dict[object, int]:
         return {key: g.pool.n_free for key, g in self.groups.items()}
@@ -262,16 +272,21 @@ class CacheManager:
         self._ok(self._lib.fxh_commit_step(self._h, n, ip, ctypes.cast(ctypes.addressof(arr) + 4 * n, type(ip))),
                  list(slots))
 
+    @staticmethod
+    def _key(g):
+        return g.window if not g.keep_first else (g.window, g.keep_first)
+
     def held_pages(self, slot: int) -> Dict[object, List[int]]:
         out = {}
         for g in self._order:
             a, b = self._lib.fxh_first_page(self._h, g.index, slot), self._lib.fxh_n_logical(self._h, g.index, slot)
-            out[g.window] = [int(p) for p in g.table[slot, a:b]]
+            kept = min(self._lib.fxh_keep_pages(self._h, g.index), a, b)      # the pages of the kept first positions
+            out[self._key(g)] = [int(p) for p in g.table[slot, :kept]] + [int(p) for p in g.table[slot, a:b]]
         return out
 
     @property
     def peak_pages(self) -> Dict[object, int]:
-        return {g.window: self._lib.fxh_peak_pages(self._h, g.index) for g in self._order}
+        return {self._key(g): self._lib.fxh_peak_pages(self._h, g.index) for g in self._order}
 
     # ---- device side ----------------------------------------------------------
     def sync_tables(self) -> None:
@@ -297,6 +312,7 @@ class CacheManager:
             state=self._state[cache_index],
             writes=writes,
             window=g.window if g is not None else None,
+            keep_first=g.keep_first if g is not None else 0,
             states=self._named_state[cache_index],
             table_host=g.table if g is not None else None,
         )

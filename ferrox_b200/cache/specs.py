@@ -44,12 +44,14 @@ class PagedTensorSpec:
 class PagedSpec:
     tensors: Tuple[PagedTensorSpec, ...]
     window: Optional[int] = None  # None: every earlier position stays readable
+    keep_first: int = 0  # with a window: the first positions of a request that stay readable beside the window
 
 
-def KvCacheSpec(n_kv_heads: int, head_dim: int, window: Optional[int] = None) -> PagedSpec:
+def KvCacheSpec(n_kv_heads: int, head_dim: int, window: Optional[int] = None, keep_first: int = 0) -> PagedSpec:
     """Keys and values of an attention layer: ``k`` and ``v``, each [n_pages, n_kv_heads, page_size, head_dim]."""
     shape = (int(n_kv_heads), int(head_dim))
-    return PagedSpec((PagedTensorSpec("k", shape, lead_dims=1), PagedTensorSpec("v", shape, lead_dims=1)), window)
+    return PagedSpec((PagedTensorSpec("k", shape, lead_dims=1), PagedTensorSpec("v", shape, lead_dims=1)), window,
+                     int(keep_first) if window is not None else 0)
 
 
 @dataclass(frozen=True)

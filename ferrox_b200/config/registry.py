@@ -18,16 +18,21 @@ from .schema import ConfigError, load_json
 class Architecture:
     name: str
     config_from_json: Callable[[dict], object]  # dict -> typed config (raises ConfigError)
-    model_spec: Callable[[object], object]  # typed config -> parts.specs.ModelSpec
+    model_spec: Callable[..., object]  # typed config -> parts.specs.ModelSpec
+    reads_shapes: bool = False  # model_spec(config, tensor_shapes) also takes the checkpoint's name -> shape table
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_from_json, model_spec, *, replace: bool = False) -> None:
+def register_architecture(name: str, config_from_json, model_spec, *, replace: bool = False,
+                          reads_shapes: bool = False) -> None:
+    """``reads_shapes``: a design that leaves a size to the shapes of its tensors; its ``model_spec(config,
+    tensor_shapes)`` is then given the checkpoint's name -> shape table (None when there is no checkpoint, as in the
+    random-weights mode, where the configuration or a default has to say)."""
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, config_from_json, model_spec)
+    _ARCHITECTURES[name] = Architecture(name, config_from_json, model_spec, reads_shapes)
 
 
 def known_architectures() -> list:
@@ -48,10 +53,12 @@ def architecture_of(obj: dict, where: str = "config.json") -> Architecture:
     return _ARCHITECTURES[name]
 
 
-def resolve(config) -> tuple:
-    """``config`` is a model folder, a path to a config.json, or the parsed dict.
-    Returns (typed config, ModelSpec)."""
+def resolve(config, tensor_shapes=None) -> tuple:
+    """``config`` is a model folder, a path to a config.json, or the parsed dict; ``tensor_shapes`` the checkpoint's
+    name -> shape table where there is one.  Returns (typed config, ModelSpec)."""
     obj = load_json(config) if isinstance(config, str) else config
     arch = architecture_of(obj)
     typed = arch.config_from_json(obj)
+    if arch.reads_shapes:
+        return typed, arch.model_spec(typed, tensor_shapes)
     return typed, arch.model_spec(typed)

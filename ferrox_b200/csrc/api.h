@@ -46,7 +46,7 @@ int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_page
                           int dtype, const int* block_table, int table_width, int page_size, const int* positions,
                           const int* token_seq, const int* seq_slot, void* out, long ldo, long ldoh, int n_tokens,
                           int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale, float softcap,
-                          const float* slopes, void* stream);
+                          const float* slopes, int keep_first, void* stream);
 
 // the same operation in bfloat16 on the tensor cores (attention_general_mma.cu); items: int32 [n_items, 5] = (first flat
 // token, tokens, entry, first query head, heads) or nullptr (one token a tile, n_items = tokens)
@@ -55,7 +55,7 @@ int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages
                          const long* kv_strides, const int* block_table, int table_width, int page_size, const int* positions,
                          const int* token_seq, const int* seq_slot, const int* items, int n_items, void* out, long ldo,
                          long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale,
-                         const float* slopes, int n_splits, float* part_o, float* part_ml, void* stream);
+                         const float* slopes, int n_splits, float* part_o, float* part_ml, int keep_first, void* stream);
 
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                             const int* block_table, int table_width, int page_size, const int* items, int n_items,
@@ -145,7 +145,7 @@ int fx_decode_attention(const void* q, long ldq, const void* k_pages, const void
 int fx_qk_norm_store(void* qkv, int dtype, long ld, const int* positions, const int* token_seq, const int* seq_slot,
                      const void* wq, const void* wk, int w_dtype, float eps, float temp_coef, int temp_every, void* k_pages,
                      void* v_pages, const int* block_table, int table_width, int page_size, int n_tokens, int n_heads,
-                     int n_kv_heads, int key_dim, int value_dim, int write_cache, int* status, void* stream);
+                     int n_kv_heads, int key_dim, int value_dim, int write_cache, int* status, float v_eps, void* stream);
 int fx_latent_prep(void* q, long ldq, const void* dkv, long ld_dkv, int dtype, const int* positions,
                    const int* token_seq, const int* seq_slot, const void* wc, int w_dtype, float eps, const float* cos_sin,
                    int rot_dims, void* q_plain, void* q_full, void* pages, const int* block_table, int table_width,
@@ -176,8 +176,8 @@ int fx_sample(float* work, long ld, int n_rows, int vocab, const float* temperat
 // Layer norm without bias (layernorm.cu): out = (x - mean) / sqrt(var + eps) * w over rows of the 32-bit residual
 // stream (`rows` optional: which rows; out may be x itself).  fx_layernorm_residual: z = s1 y1 (+ s2 y2);
 // h += ln(z) w_post; and, if w_next is given, x_out = ln(h) w_next on the new rows.  fx_scale: x *= scale.
-int fx_layernorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out, int out_dtype,
-                 int n_rows, int hidden, void* stream);
+int fx_layernorm(const float* x, const int* rows, const void* w, int w_dtype, const void* bias, int b_dtype, float eps,
+                 void* out, int out_dtype, int n_rows, int hidden, void* stream);
 int fx_layernorm_residual(float* h, const void* y1, int y1_dtype, float s1, const void* y2, int y2_dtype, float s2,
                           const void* w_post, int wp_dtype, float eps, const void* w_next, int wn_dtype, float eps_next,
                           void* x_out, int x_dtype, int n_rows, int hidden, void* stream);
@@ -197,7 +197,35 @@ int fx_state_scan(const void* q, long ldq, const void* k, long ldk, const void* 
                   const int* seq_slot, int n_tokens, int n_entries, int H, int G, int D, int V, void* stream);
 int fx_set_scan_lanes(int lanes);   // lanes that share a state column, fixed for measurements (0: the launcher's choice)
 int fx_gated_group_norm(const float* x, const void* gate, int gate_dtype, long ldg, const void* w, int w_dtype, float eps,
-                        int act, void* out, int out_dtype, int n_tokens, int groups, int width, void* stream);
+                        int act, void* out, int out_dtype, int n_tokens, int groups, int width, long w_stride,
+                        void* stream);
+
+// The generalized delta rule (general_delta.cu).  fx_general_delta_prep: per (token, head) the unit key
+// u = k / sqrt(sum k^2 + 1e-6), a u with a = sigmoid(a_pre + a_bias), and the decay
+// w = exp(-rate * sigmoid(w2 . tanh(w1_out) + w0)), from 32-bit rows.  fx_general_delta_scan: over every entry's
+// tokens in order, S <- diag(w) S - (a u)(u^T S) + k v^T (both terms read the old S), out = S^T r; state
+// [slots, H, D(value), D(key)] 32-bit.
+int fx_general_delta_prep(const float* k, long ldk, const float* a_pre, long lda, const float* w1_out, long ldw1,
+                          const void* w2, int w2_dtype, const void* w0, int w0_dtype, const void* a_bias, int ab_dtype,
+                          float rate, float* u, float* au, float* w, int n_tokens, int H, int D, int rank, void* stream);
+int fx_general_delta_scan(const float* r, long ldr, const float* k, long ldk, const float* v, long ldv, const float* u,
+                          const float* au, const float* w, float* state, float* out, long ldo, const int* token_seq,
+                          const int* seq_slot, int n_tokens, int n_entries, int H, int D, void* stream);
+
+// The input convolution of a mixer (input_conv.cu): out[t] = x[t] + sum_j w[:, j] x[t - taps + 1 + j] over the
+// tokens of a request, the inputs before the step from tail [slots, taps - 1, channels] (32-bit, oldest first).
+// update_tail: every entry brings exactly one token and the kernel moves the tail on itself.
+int fx_input_conv(const void* x, int dtype, long ldx, const void* w, int w_dtype, int taps, float* tail,
+                  const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int channels,
+                  int update_tail, void* stream);
+// out[t] = table[ids[t]] + pos_table[positions[t]] in 32 bits; status 1: an id outside the vocabulary, 4: a position
+// outside the table.
+int fx_embed_pos(const void* table, int dtype, const int* ids, const void* pos_table, int pos_dtype, const int* positions,
+                 float* out, int n_tokens, int hidden, int vocab, int n_positions, int* status, void* stream);
+// x <- cap * tanh(x / cap), 32-bit, in place.
+int fx_softcap(float* x, long n, float cap, void* stream);
+// x <- max(x, 0)^2 in place, rows of `n` elements with row stride ld.
+int fx_relu_square(void* x, int dtype, long ld, int rows, int n, void* stream);
 
 #ifdef __cplusplus
 }

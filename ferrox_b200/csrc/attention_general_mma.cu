@@ -19,6 +19,10 @@
 // In that form a token's visible keys may be cut into n_splits runs (fx_split_range: equal runs, whatever the
 // context length), one block each, so that a step of few tokens fills the machine; a block then leaves its
 // unnormalised sums and its (maximum, sum) in scratch and a second kernel adds a row's runs up.
+//
+// keep_first (with a window): the first keep_first positions of a request stay visible to every query beside its
+// window.  The key blocks that hold them and lie wholly before the first window block are taken first (blocks
+// 0 .. n_kept - 1 of the loop), then the window's blocks; of a decoding token's runs, run 0 takes them.
 #include "common.cuh"
 #include "api.h"
 
@@ -60,6 +64,7 @@ struct GArgs {
     const int* items;
     bf16* out; long ldo, ldoh;
     int n_heads, n_kv_heads, key_dim, value_dim, window;
+    int keep_first;   // (window > 0) positions 0 .. keep_first - 1 stay visible beside the window
     float scale_log2e;
     const float* slopes;
     int alias;        // the values are the leading columns of the key rows: one copy in shared memory serves both
@@ -107,14 +112,20 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
     const int kchunks = a.key_dim / 8, vchunks = a.value_dim / 8;   // 16-byte chunks per row
     int last_pos = pos0 + n_tok - 1;
     int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;   // first key any row may see
+    int keep = a.keep_first;   // kept first positions this block takes
     if (a.n_splits > 1) {      // (one token a tile) this block's run of the token's keys
         int k_begin, k_end;
         fx_split_range(pos0, key_lo, blockIdx.z, a.n_splits, 0, k_begin, k_end);
         if (k_begin >= k_end) return;      // nothing of this run is visible: the merge skips it by the same rule
+        if (blockIdx.z > 0) keep = 0;      // (run 0 always has keys: it begins at the token's first visible key)
         key_lo = k_begin; last_pos = k_end - 1;
     }
     const int kb_begin = (key_lo / BKEY) * BKEY;
-    const int n_blocks = (last_pos - kb_begin) / BKEY + 1;
+    // key blocks of the kept first positions that lie wholly before the first window block (what of them falls into
+    // a window block is admitted there by the mask)
+    const int n_kept = (min(keep, kb_begin) + BKEY - 1) / BKEY;
+    const int n_blocks = n_kept + (last_pos - kb_begin) / BKEY + 1;
+    auto block_start = [&](int blk) { return blk < n_kept ? blk * BKEY : kb_begin + (blk - n_kept) * BKEY; };
 
     // ---- Q rows -> shared memory (rows past the tile's end are zero) ----------------
     for (int c = threadIdx.x; c < BQ * kchunks; c += NTHREADS) {
@@ -124,12 +135,12 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
         cp_async16(q_u + r * pk + ch * 16, src, r < rows ? 16 : 0);
     }
     auto load_kv = [&](int blk, int buf) {
-        const int kb = kb_begin + blk * BKEY;
+        const int kb = block_start(blk);
         for (int c = threadIdx.x; c < BKEY * kchunks; c += NTHREADS) {
             const int r = c / kchunks, ch = c - r * kchunks;
             const int key = kb + r;
             int page = -1;
-            if (key <= last_pos && key >= key_lo) page = table[key / a.page_size];
+            if (key <= last_pos && (key >= key_lo || key < keep)) page = table[key / a.page_size];
             const bool ok = page >= 0;
             const long at = ok ? (long)page * a.k_page_stride + (long)kvh * a.k_head_stride + (long)(key % a.page_size) * a.ldk : 0;
             cp_async16(k_u + (buf * BKEY + r) * pk + ch * 16, a.k_pages + at + ch * 8, ok ? 16 : 0);
@@ -139,7 +150,7 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
             const int r = c / vchunks, ch = c - r * vchunks;
             const int key = kb + r;
             int page = -1;
-            if (key <= last_pos && key >= key_lo) page = table[key / a.page_size];
+            if (key <= last_pos && (key >= key_lo || key < keep)) page = table[key / a.page_size];
             const bool ok = page >= 0;
             const long at = ok ? (long)page * a.v_page_stride + (long)kvh * a.v_head_stride + (long)(key % a.page_size) * a.ldv : 0;
             cp_async16(v_u + (buf * BKEY + r) * pv + ch * 16, a.v_pages + at + ch * 8, ok ? 16 : 0);
@@ -178,8 +189,8 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
         cp_wait<1>();
         __syncthreads();
 
-        const int kb = kb_begin + blk * BKEY;
-        const bool warp_active = qrow0 < rows && my_cols > 0 && kb <= w_last && kb + BKEY - 1 >= w_lo;
+        const int kb = block_start(blk);
+        const bool warp_active = qrow0 < rows && my_cols > 0 && kb <= w_last && (kb + BKEY - 1 >= w_lo || kb < keep);
         if (warp_active) {
             // ---- S = Q K^T : 16 x 32 per warp ---------------------------------------
             float s[BKEY / 8][4];
@@ -205,9 +216,9 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = kb + j * 8 + 2 * t4 + e;
-                    s[j][e] = (key > hi0 || key < lo0) ? -INFINITY
+                    s[j][e] = (key > hi0 || (key < lo0 && key >= keep)) ? -INFINITY
                                                           : fmaf(-sl0, (float)(p_row0 - key), s[j][e] * a.scale_log2e);
-                    s[j][2 + e] = (key > hi1 || key < lo1) ? -INFINITY
+                    s[j][2 + e] = (key > hi1 || (key < lo1 && key >= keep)) ? -INFINITY
                                                               : fmaf(-sl1, (float)(p_row1 - key), s[j][2 + e] * a.scale_log2e);
                     mx0 = fmaxf(mx0, s[j][e]);
                     mx1 = fmaxf(mx1, s[j][2 + e]);
@@ -366,7 +377,7 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
                                     const int* positions, const int* token_seq, const int* seq_slot, const int* items,
                                     int n_items, void* out, long ldo, long ldoh, int n_heads, int n_kv_heads,
                                     int key_dim, int value_dim, int window, float scale, const float* slopes,
-                                    int n_splits, float* part_o, float* part_ml, void* stream)
+                                    int n_splits, float* part_o, float* part_ml, int keep_first, void* stream)
 {
     if (n_items <= 0) return FX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
@@ -386,6 +397,7 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
     a.positions = positions; a.token_seq = token_seq; a.seq_slot = seq_slot; a.items = items;
     a.out = (bf16*)out; a.ldo = ldo; a.ldoh = ldoh;
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.window = window;
+    a.keep_first = (window > 0 && keep_first > 0) ? keep_first : 0;
     a.scale_log2e = scale * 1.4426950408889634f; a.slopes = slopes; a.alias = alias;
     a.n_splits = n_splits > 1 ? n_splits : 1; a.part_o = part_o; a.part_ml = part_ml;
     if (a.n_splits > 1 && (items || !part_o || !part_ml || a.n_splits > 65535)) return FX_ERR_SIZE;

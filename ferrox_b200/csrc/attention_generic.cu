@@ -27,6 +27,8 @@
 // token stride and a head stride, so that rows laid out head by head ([head][token][dim]) are read as they lie.
 // `slopes` (optional, one per head): the score of key j for the query at position i is lowered by
 // slopes[h] * (i - j), a bias that grows with the distance.
+// `keep_first` (with a window): the first keep_first positions of the request stay visible beside the window; they
+// are taken first, in blocks of 32 from position 0, then the window's keys as ever.
 #include "common.cuh"
 #include "api.h"
 
@@ -42,7 +44,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     long ldk, long ldv, const int* __restrict__ block_table, int table_width, int page_size,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
     T* __restrict__ out, long ldo, long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window,
-    float scale, float softcap, const float* __restrict__ slopes)
+    float scale, float softcap, const float* __restrict__ slopes, int keep_first)
 {
     __shared__ float q_s[WARPS][MAX_DK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -63,9 +65,16 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
 #pragma unroll
     for (int i = 0; i < NV; ++i) acc[i] = 0.f;
 
-    for (int kb = (lo / 32) * 32; kb <= pos; kb += 32) {
+    // the kept first positions that the window no longer covers: keys 0 .. kept_end - 1
+    const int kept_end = keep_first < lo ? keep_first : lo;
+    const int kept_blocks = (kept_end + 31) / 32;
+    const int win_kb = (lo / 32) * 32;
+    const int n_blocks = kept_blocks + (pos - win_kb) / 32 + 1;
+    for (int blk = 0; blk < n_blocks; ++blk) {
+        const bool kept = blk < kept_blocks;
+        const int kb = kept ? blk * 32 : win_kb + (blk - kept_blocks) * 32;
         const int key = kb + lane;
-        bool valid = key >= lo && key <= pos;
+        bool valid = kept ? key < kept_end : (key >= lo && key <= pos);
         long place = -1;      // (page, kv head, position in the page) as one index
         float s = -INFINITY;
         const int page = valid ? table[key / page_size] : -1;
@@ -112,13 +121,14 @@ template <typename T>
 int launch_paged(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk, long ldv,
                  const int* block_table, int table_width, int page_size, const int* positions, const int* token_seq,
                  const int* seq_slot, void* out, long ldo, long ldoh, int n_tokens, int n_heads, int n_kv_heads,
-                 int key_dim, int value_dim, int window, float scale, float softcap, const float* slopes, cudaStream_t s)
+                 int key_dim, int value_dim, int window, float scale, float softcap, const float* slopes, int keep_first,
+                 cudaStream_t s)
 {
     dim3 grid(n_tokens, (unsigned)fx_cdiv(n_heads, WARPS));
 #define FX_GO(NV)                                                                                                     \
     paged_attention_kernel<T, NV><<<grid, WARPS * 32, 0, s>>>((const T*)q, ldq, ldqh, (const T*)k_pages,              \
         (const T*)v_pages, ldk, ldv, block_table, table_width, page_size, positions, token_seq, seq_slot, (T*)out,    \
-        ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap, slopes)
+        ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap, slopes, keep_first)
     if (value_dim <= 64) FX_GO(2);
     else if (value_dim <= 128) FX_GO(4);
     else if (value_dim <= 256) FX_GO(8);
@@ -136,9 +146,10 @@ extern "C" int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const v
                                      int page_size, const int* positions, const int* token_seq, const int* seq_slot,
                                      void* out, long ldo, long ldoh, int n_tokens, int n_heads, int n_kv_heads,
                                      int key_dim, int value_dim, int window, float scale, float softcap,
-                                     const float* slopes, void* stream)
+                                     const float* slopes, int keep_first, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (keep_first < 0 || window <= 0) keep_first = 0;
     if (key_dim > MAX_DK || value_dim > MAX_DV || key_dim <= 0 || value_dim <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || ldk < key_dim || ldv < value_dim)
         return FX_ERR_SIZE;
@@ -146,11 +157,11 @@ extern "C" int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const v
     if (dtype == FX_F32)
         return launch_paged<float>(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, table_width, page_size,
                                    positions, token_seq, seq_slot, out, ldo, ldoh, n_tokens, n_heads, n_kv_heads,
-                                   key_dim, value_dim, window, scale, softcap, slopes, s);
+                                   key_dim, value_dim, window, scale, softcap, slopes, keep_first, s);
     if (dtype == FX_BF16)
         return launch_paged<bf16>(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, table_width, page_size,
                                   positions, token_seq, seq_slot, out, ldo, ldoh, n_tokens, n_heads, n_kv_heads,
-                                  key_dim, value_dim, window, scale, softcap, slopes, s);
+                                  key_dim, value_dim, window, scale, softcap, slopes, keep_first, s);
     return FX_ERR_DTYPE;
 }
 
@@ -163,5 +174,5 @@ extern "C" int fx_paged_attention(const void* q, long ldq, const void* k_pages, 
 {
     return fx_paged_attention_ex(q, ldq, head_dim, k_pages, v_pages, head_dim, head_dim, dtype, block_table, table_width,
                                  page_size, positions, token_seq, seq_slot, out, ldo, head_dim, n_tokens, n_heads,
-                                 n_kv_heads, head_dim, head_dim, window, scale, softcap, nullptr, stream);
+                                 n_kv_heads, head_dim, head_dim, window, scale, softcap, nullptr, 0, stream);
 }

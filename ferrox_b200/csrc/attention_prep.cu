@@ -13,6 +13,8 @@ namespace {
 //   q <- q / sqrt(mean(q^2) + eps) * wq * (1 + coef * ln(floor((pos + 1) / every) + 1))
 //   k <- k / sqrt(mean(k^2) + eps) * wk                      (wq, wk: [D], shared by the heads; null: no norm)
 // then k and v go to the pages, [page][kv head][position][D] and [page][kv head][position][V].
+// v_eps >= 0: every value head is divided by its root mean square first, v / sqrt(mean(v^2) + v_eps), no weight,
+// and is cached so.
 // One block a token, a warp a head.
 template <typename T>
 __global__ void qk_norm_store_kernel(T* __restrict__ qkv, long ld, const int* __restrict__ positions,
@@ -20,7 +22,7 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qkv, long ld, const int* __
                                      const void* __restrict__ wq, const void* __restrict__ wk, int w_dtype, float eps,
                                      float temp_coef, int temp_every, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      const int* __restrict__ block_table, int table_width, int page_size, int H, int G,
-                                     int D, int V, int write_cache, int* __restrict__ status)
+                                     int D, int V, int write_cache, int* __restrict__ status, float v_eps)
 {
     fx_pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -57,6 +59,18 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qkv, long ld, const int* __
     }
     if (place < 0) return;
     const T* v = row + (long)(H + G) * D;
+    if (v_eps >= 0.f) {
+        for (int g = warp; g < G; g += n_warps) {
+            const T* x = v + (long)g * V;
+            float ss = 0.f;
+            for (int i = lane; i < V; i += 32) { const float f = to_f32(x[i]); ss = fmaf(f, f, ss); }
+            ss = warp_sum(ss);
+            const float r = sqrtf(ss / (float)V + v_eps);
+            T* vp = v_pages + (place + (long)g * page_size) * V;
+            for (int i = lane; i < V; i += 32) vp[i] = from_f32<T>(to_f32(x[i]) / r);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < G * V; idx += blockDim.x) {
         const int g = idx / V, i = idx - g * V;
         v_pages[(place + (long)g * page_size) * V + i] = v[idx];
@@ -183,7 +197,7 @@ extern "C" int fx_qk_norm_store(void* qkv, int dtype, long ld, const int* positi
                                 const int* seq_slot, const void* wq, const void* wk, int w_dtype, float eps,
                                 float temp_coef, int temp_every, void* k_pages, void* v_pages, const int* block_table,
                                 int table_width, int page_size, int n_tokens, int n_heads, int n_kv_heads, int key_dim,
-                                int value_dim, int write_cache, int* status, void* stream)
+                                int value_dim, int write_cache, int* status, float v_eps, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (key_dim <= 0 || value_dim <= 0 || page_size <= 0 || n_heads <= 0 || n_kv_heads <= 0) return FX_ERR_SIZE;
@@ -192,7 +206,7 @@ extern "C" int fx_qk_norm_store(void* qkv, int dtype, long ld, const int* positi
 #define FX_GO(T)                                                                                                      \
     fx_launch_pdl(qk_norm_store_kernel<T>, n_tokens, nt, 0, s, (T*)qkv, ld, positions, token_seq, seq_slot, wq, wk,  \
                   w_dtype, eps, temp_coef, temp_every, (T*)k_pages, (T*)v_pages, block_table, table_width, page_size, \
-                  n_heads, n_kv_heads, key_dim, value_dim, write_cache, status)
+                  n_heads, n_kv_heads, key_dim, value_dim, write_cache, status, v_eps)
     if (dtype == FX_F32) FX_GO(float);
     else if (dtype == FX_BF16) FX_GO(bf16);
     else return FX_ERR_DTYPE;

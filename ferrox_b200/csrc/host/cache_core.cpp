@@ -6,7 +6,10 @@
 // list: the page freed last is handed out first), one block table per request slot
 // ([max_slots][width] int32, -1 = no page) and, for each slot, the range of logical
 // pages still held [first_page, n_logical).  A group with a window gives back, at
-// commit, the pages whose every position is older than new_len - window + 1.
+// commit, the pages whose every position is older than new_len - window + 1; a group
+// whose window also keeps the first `keep_first` positions of a request readable
+// never gives back the pages that hold them (logical pages below keep_pages stay
+// mapped beside the held range).
 // reserve() is all-or-nothing over all groups.
 //
 // Reference: crates/ferrox-core/src/cache.rs:331-405 (shared pages, LIFO free list),
@@ -20,6 +23,7 @@ namespace {
 
 struct Group {
     int window;  // -1: every earlier position stays readable
+    int keep_pages = 0;  // logical pages at the start of a request that a windowed group never gives back
     int n_pages;
     std::vector<int> free_list;      // back() is handed out next
     std::vector<uint8_t> held;
@@ -73,6 +77,16 @@ void* fxh_cache_create(int n_groups, const int* windows, const int* n_pages, int
 
 void fxh_cache_destroy(void* h) { delete static_cast<Cache*>(h); }
 
+// The first keep_first positions of every request stay readable in this (windowed) group.  Set before any
+// request is opened.
+int fxh_set_keep_first(void* h, int group, int keep_first)
+{
+    Cache* c = static_cast<Cache*>(h);
+    if (group < 0 || group >= (int)c->groups.size() || keep_first < 0) return FXH_BAD_SLOT;
+    c->groups[group].keep_pages = pages_for(*c, keep_first);
+    return FXH_OK;
+}
+
 int fxh_open(void* h)
 {
     Cache* c = static_cast<Cache*>(h);
@@ -92,7 +106,7 @@ int fxh_close(void* h, int slot)
     if (!check_live(c, slot)) return FXH_BAD_SLOT;
     for (Group& G : c->groups) {
         int32_t* row = G.table.data() + (size_t)slot * c->width;
-        for (int j = G.first_page[slot]; j < G.n_logical[slot]; ++j) {
+        for (int j = 0; j < G.n_logical[slot]; ++j) {      // (pages given back already are -1)
             const int p = row[j];
             if (p < 0) continue;
             if (p >= G.n_pages || !G.held[p]) return FXH_CORRUPT;
@@ -167,8 +181,10 @@ int fxh_commit(void* h, int slot, int new_len)
         int upto = first_needed / c->page_size;
         if (upto > G.n_logical[slot]) upto = G.n_logical[slot];
         int32_t* row = G.table.data() + (size_t)slot * c->width;
-        if (upto > G.first_page[slot]) {
-            for (int j = G.first_page[slot]; j < upto; ++j) {
+        int from = G.first_page[slot] > G.keep_pages ? G.first_page[slot] : G.keep_pages;   // kept pages stay
+        if (from > G.n_logical[slot]) from = G.n_logical[slot];
+        if (upto > from) {
+            for (int j = from; j < upto; ++j) {
                 const int p = row[j];
                 if (p < 0 || p >= G.n_pages || !G.held[p]) return FXH_CORRUPT;
                 G.held[p] = 0;
@@ -227,6 +243,7 @@ int fxh_free_slots(void* h) { return (int)static_cast<Cache*>(h)->free_slots.siz
 int fxh_seq_len(void* h, int slot) { return static_cast<Cache*>(h)->seq_len[slot]; }
 int fxh_first_page(void* h, int group, int slot) { return static_cast<Cache*>(h)->groups[group].first_page[slot]; }
 int fxh_n_logical(void* h, int group, int slot) { return static_cast<Cache*>(h)->groups[group].n_logical[slot]; }
+int fxh_keep_pages(void* h, int group) { return static_cast<Cache*>(h)->groups[group].keep_pages; }
 int fxh_is_live(void* h, int slot) { return check_live(static_cast<Cache*>(h), slot); }
 
 // rows of group's table whose device copy is stale; clears the marks.  Returns the count.
@@ -250,7 +267,7 @@ int fxh_check(void* h)
             const int32_t* row = G.table.data() + (size_t)s * c->width;
             for (int j = 0; j < c->width; ++j) {
                 const int p = row[j];
-                const bool inside = c->live[s] && j >= G.first_page[s] && j < G.n_logical[s];
+                const bool inside = c->live[s] && j < G.n_logical[s] && (j >= G.first_page[s] || j < G.keep_pages);
                 if (p >= 0 && !inside) return 1;                 // a page mapped outside a live slot's held range
                 if (p < 0 && inside) return 2;                   // a hole in the held range
                 if (p >= 0) {

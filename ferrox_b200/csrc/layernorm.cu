@@ -1,5 +1,5 @@
-// Layer norm without bias over rows of the 32-bit residual stream, and the form that a block with norms on both
-// sides of its sublayers needs: the sublayer's output is normed, added to the residual stream, and the new row is
+// Layer norm (a weight, and a bias where the caller has one) over rows of the 32-bit residual stream, and the form
+// that a block with norms on both sides of its sublayers needs: the sublayer's output is normed, added to the residual stream, and the new row is
 // normed again for the sublayer that follows, in one pass over the row.
 //
 //   ln(z)[i] = (z[i] - mean(z)) / sqrt(mean((z - mean(z))^2) + eps) * w[i]
@@ -30,8 +30,8 @@ __device__ __forceinline__ RowStats row_stats(F value, int n, float eps, float* 
 
 template <typename OT>
 __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(
-    const float* x, const int* __restrict__ rows, const void* __restrict__ w, int w_dtype, float eps,
-    OT* out, int hidden)
+    const float* x, const int* __restrict__ rows, const void* __restrict__ w, int w_dtype,
+    const void* __restrict__ bias, int b_dtype, float eps, OT* out, int hidden)
 {
     __shared__ float scratch[33];
     fx_pdl_wait();
@@ -39,8 +39,11 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(
     const float* xr = x + (long)(rows ? rows[r] : r) * hidden;
     const RowStats st = row_stats([&](int i) { return xr[i]; }, hidden, eps, scratch);
     OT* o = out + (long)r * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        o[i] = from_f32<OT>((xr[i] - st.mean) * st.rstd * load_any(w, w_dtype, i));
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = (xr[i] - st.mean) * st.rstd * load_any(w, w_dtype, i);
+        if (bias) v += load_any(bias, b_dtype, i);
+        o[i] = from_f32<OT>(v);
+    }
 }
 
 // z = s1 * y1 (+ s2 * y2);  h += ln(z) * w_post;  x_out = ln(h) * w_next (if asked for).
@@ -86,14 +89,14 @@ inline int ln_threads(int hidden, int n_rows)
 
 }  // namespace
 
-extern "C" int fx_layernorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out,
-                            int out_dtype, int n_rows, int hidden, void* stream)
+extern "C" int fx_layernorm(const float* x, const int* rows, const void* w, int w_dtype, const void* bias, int b_dtype,
+                            float eps, void* out, int out_dtype, int n_rows, int hidden, void* stream)
 {
     if (n_rows <= 0) return FX_OK;
     if (hidden <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == FX_F32) fx_launch_pdl(layernorm_kernel<float>, n_rows, ln_threads(hidden, n_rows), 0, s, x, rows, w, w_dtype, eps, (float*)out, hidden);
-    else if (out_dtype == FX_BF16) fx_launch_pdl(layernorm_kernel<bf16>, n_rows, ln_threads(hidden, n_rows), 0, s, x, rows, w, w_dtype, eps, (bf16*)out, hidden);
+    if (out_dtype == FX_F32) fx_launch_pdl(layernorm_kernel<float>, n_rows, ln_threads(hidden, n_rows), 0, s, x, rows, w, w_dtype, bias, b_dtype, eps, (float*)out, hidden);
+    else if (out_dtype == FX_BF16) fx_launch_pdl(layernorm_kernel<bf16>, n_rows, ln_threads(hidden, n_rows), 0, s, x, rows, w, w_dtype, bias, b_dtype, eps, (bf16*)out, hidden);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

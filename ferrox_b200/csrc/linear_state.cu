@@ -351,11 +351,12 @@ int scan_for(const ScanArgs& a, int rpl, int n_entries, cudaStream_t s)
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// out[t, grp, i] = x[t, grp, i] / sqrt(mean_i x^2 + eps) * w[i] * act(gate[t, grp, i]); act 0: SiLU, 1: sigmoid.
+// out[t, grp, i] = x[t, grp, i] / sqrt(mean_i x^2 + eps) * w[grp * w_stride + i] * act(gate[t, grp, i]); act 0: SiLU,
+// 1: sigmoid.  w_stride 0: the groups share one weight vector; width: a weight for every element of the row.
 template <typename GT, typename OT>
 __global__ void __launch_bounds__(128) gated_group_norm_kernel(
     const float* __restrict__ x, const GT* __restrict__ gate, long ldg, const void* __restrict__ w, int w_dtype,
-    float eps, int act, OT* __restrict__ out, int groups, int width)
+    float eps, int act, OT* __restrict__ out, int groups, int width, long w_stride)
 {
     __shared__ float scratch[33];
     fx_pdl_wait();
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(
     OT* o = out + ((long)t * groups + grp) * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float gv = to_f32(gr[i]);
-        o[i] = from_f32<OT>(xr[i] * inv * load_any(w, w_dtype, i) * (act ? sigmoid_f(gv) : silu_f(gv)));
+        o[i] = from_f32<OT>(xr[i] * inv * load_any(w, w_dtype, (long)grp * w_stride + i) * (act ? sigmoid_f(gv) : silu_f(gv)));
     }
 }
 
@@ -453,18 +454,18 @@ extern "C" int fx_state_scan(const void* q, long ldq, const void* k, long ldk, c
 
 extern "C" int fx_gated_group_norm(const float* x, const void* gate, int gate_dtype, long ldg, const void* w, int w_dtype,
                                    float eps, int act, void* out, int out_dtype, int n_tokens, int groups, int width,
-                                   void* stream)
+                                   long w_stride, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     if (groups <= 0 || width <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, groups);
     if (gate_dtype == FX_F32 && out_dtype == FX_F32)
-        fx_launch_pdl(gated_group_norm_kernel<float, float>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (float*)out, groups, width);
+        fx_launch_pdl(gated_group_norm_kernel<float, float>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (float*)out, groups, width, w_stride);
     else if (gate_dtype == FX_F32 && out_dtype == FX_BF16)
-        fx_launch_pdl(gated_group_norm_kernel<float, bf16>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width);
+        fx_launch_pdl(gated_group_norm_kernel<float, bf16>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width, w_stride);
     else if (gate_dtype == FX_BF16 && out_dtype == FX_BF16)
-        fx_launch_pdl(gated_group_norm_kernel<bf16, bf16>, grid, 128, 0, s, x, (const bf16*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width);
+        fx_launch_pdl(gated_group_norm_kernel<bf16, bf16>, grid, 128, 0, s, x, (const bf16*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width, w_stride);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -71,7 +71,7 @@ class Engine:
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **cache_opts) -> "Engine":
         _require_cuda(device)
-        config, spec = resolve(load_json(folder))
+        config, spec = resolve(load_json(folder), wl.folder_shapes(folder))
         model = build_model(spec)
         rt = Runtime(torch.device(device), _dtype(dtype))
         src, files = wl.open_folder(folder, model.tensor_decls(), rt.device, rt.dtype)

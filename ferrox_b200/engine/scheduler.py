@@ -126,7 +126,9 @@ class Scheduler:
         need = (worst + self.cache.page_size - 1) // self.cache.page_size
         for key, g in self.cache.groups.items():
             # a windowed group holds at most the window plus the pages of one portion
-            floor = need if key is None else min(need, (key + self.cache.page_size - 1) // self.cache.page_size + 2)
+            ps = self.cache.page_size
+            floor = need if g.window is None else min(
+                need, (g.window + ps - 1) // ps + 2 + (g.keep_first + ps - 1) // ps)
             if floor > g.pool.n_pages:
                 raise AdmissionError(
                     f"request of up to {worst} positions needs {floor} pages, the pool has {g.pool.n_pages}")

@@ -74,7 +74,8 @@ def step(model, cache, entries: Sequence[StepEntry], *, check: bool = True, grap
             status.zero_()
             model.reset_after_fault()
             what = {1: "a token id outside the vocabulary", 2: "a position without a cache page",
-                    3: "a bounded wait that ran out inside a tensor-core kernel"}.get(code, code)
+                    3: "a bounded wait that ran out inside a tensor-core kernel",
+                    4: "a position outside the learned position table"}.get(code, code)
             raise StepFault(f"step met {what}")
     cache.commit_step(slots, counts)
     return logits

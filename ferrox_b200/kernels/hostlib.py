@@ -65,6 +65,7 @@ def load() -> ctypes.CDLL:
             sig = {
                 "fxh_cache_create": ([I, IP, IP, I, I, I, I], P),
                 "fxh_cache_destroy": ([P], None),
+                "fxh_set_keep_first": ([P, I, I], I), "fxh_keep_pages": ([P, I], I),
                 "fxh_open": ([P], I), "fxh_close": ([P, I], I),
                 "fxh_pages_needed": ([P, I, I, IP], I),
                 "fxh_reserve": ([P, I, I], I), "fxh_commit": ([P, I, I], I),

@@ -48,11 +48,12 @@ _SIGNATURES = {
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_gather_rows_scaled": [_P, _L, _P, _P, _P, _I, _P, _L, _I, _I, _I, _P],
     "fx_paged_attention_ex": [_P, _L, _L, _P, _P, _L, _L, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
-                              _F, _P, _P],
+                              _F, _P, _I, _P],
     "fx_general_attention_ok": [_I, _I, _I],
     "fx_general_attention": [_P, _L, _L, _P, _P, _L, _L, _P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I,
-                             _F, _P, _I, _P, _P, _P],
-    "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+                             _F, _P, _I, _P, _P, _I, _P],
+    "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F,
+                         _P],
     "fx_latent_prep": [_P, _L, _P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
                        _P],
     "fx_rmsnorm_rows": [_P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _P],
@@ -65,13 +66,19 @@ _SIGNATURES = {
     "fx_residual_add": [_P, _P, _I, _L, _P],
     "fx_paged_attention": [_P, _L, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _F, _P],
     "fx_glu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _I, _F, _F, _P],
-    "fx_layernorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
+    "fx_layernorm": [_P, _P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_layernorm_residual": [_P, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_scale": [_P, _L, _F, _P],
     "fx_delta_prep": [_P, _I, _L, _P, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "fx_conv_tail_update": [_P, _I, _L, _I, _I, _P, _P, _P, _I, _I, _P],
     "fx_state_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "fx_gated_group_norm": [_P, _P, _I, _L, _P, _I, _F, _I, _P, _I, _I, _I, _I, _P],
+    "fx_gated_group_norm": [_P, _P, _I, _L, _P, _I, _F, _I, _P, _I, _I, _I, _I, _L, _P],
+    "fx_general_delta_prep": [_P, _L, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _P],
+    "fx_general_delta_scan": [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+    "fx_input_conv": [_P, _I, _L, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _P],
+    "fx_embed_pos": [_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
+    "fx_softcap": [_P, _L, _F, _P],
+    "fx_relu_square": [_P, _I, _L, _I, _I, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _F, _P],
     "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P, _P,
                                 _P, _I, _P],
@@ -338,12 +345,13 @@ def silu_mul(gu, out, stream=None, activation="silu"):
     return out
 
 
-def layernorm(x, weight, eps, out, rows=None, stream=None):
-    """out = (x - mean) / sqrt(var + eps) * weight over rows of the 32-bit stream ``x`` (``out`` may be ``x``)."""
+def layernorm(x, weight, eps, out, rows=None, stream=None, bias=None):
+    """out = (x - mean) / sqrt(var + eps) * weight (+ bias) over rows of the 32-bit stream ``x`` (``out`` may be
+    ``x``)."""
     if x.dtype != torch.float32:
         raise KernelError("layernorm reads the 32-bit residual stream")
-    call("fx_layernorm", _ptr(x), _ptr(rows), _ptr(weight), code(weight), float(eps), _ptr(out), code(out), out.shape[0],
-         x.shape[1], stream if stream is not None else stream_ptr())
+    call("fx_layernorm", _ptr(x), _ptr(rows), _ptr(weight), code(weight), _ptr(bias), code(bias) if bias is not None else 0,
+         float(eps), _ptr(out), code(out), out.shape[0], x.shape[1], stream if stream is not None else stream_ptr())
     return out
 
 
@@ -413,11 +421,76 @@ GROUP_NORM_GATES = {"silu": 0, "sigmoid": 1}
 
 def gated_group_norm(x, gate, weight, eps, gate_activation, out, groups, width, stream=None):
     """out[t, g, :] = x[t, g, :] / sqrt(mean(x[t, g, :]^2) + eps) * weight * act(gate[t, g, :]); ``x`` 32-bit
-    [T, groups*width], ``gate`` a row view of the same width, ``weight`` [width]."""
+    [T, groups*width], ``gate`` a row view of the same width, ``weight`` [width] (shared by the groups) or
+    [groups*width] (a weight for every element of the row)."""
+    if weight.numel() not in (width, groups * width):
+        raise KernelError("gated_group_norm: a weight per group element, or one for every element of the row")
     call("fx_gated_group_norm", _ptr(x), _ptr(gate), code(gate), _rows(gate), _ptr(weight), code(weight), float(eps),
          GROUP_NORM_GATES[gate_activation], _ptr(out), code(out), x.shape[0], int(groups), int(width),
+         int(width) if weight.numel() != width else 0, stream if stream is not None else stream_ptr())
+    return out
+
+
+def general_delta_prep(k, a_pre, w1_out, w2, w0, a_bias, rate, u, au, w, H, D, stream=None):
+    """What the generalized delta rule needs before its recurrence, per (token, head), from 32-bit row views ``k``
+    [T, H*D], ``a_pre`` [T, H*D] and ``w1_out`` [T, rank]: the unit key u = k / sqrt(sum k^2 + 1e-6), a u with
+    a = sigmoid(a_pre + a_bias), and the decay w = exp(-rate sigmoid(w2 . tanh(w1_out) + w0)); ``u``, ``au``, ``w``
+    contiguous 32-bit [T, H*D]."""
+    for t in (k, a_pre, w1_out, u, au, w):
+        if t.dtype != torch.float32:
+            raise KernelError("general_delta_prep: what enters the recurrence is 32-bit")
+    T, rank = k.shape[0], w1_out.shape[1]
+    call("fx_general_delta_prep", _ptr(k), _rows(k), _ptr(a_pre), _rows(a_pre), _ptr(w1_out), _rows(w1_out), _ptr(w2),
+         code(w2), _ptr(w0), code(w0), _ptr(a_bias), code(a_bias), float(rate), _ptr(u), _ptr(au), _ptr(w), T, int(H),
+         int(D), int(rank), stream if stream is not None else stream_ptr())
+
+
+def general_delta_scan(r, k, v, u, au, w, state, out, token_seq, seq_slot, n_entries, H, D, stream=None):
+    """The generalized delta rule over every entry's tokens in order: S = diag(w) S - (a u)(u^T S) + k v^T,
+    out = S^T r.  ``r``, ``k``, ``v`` 32-bit row views [T, H*D]; ``u``, ``au``, ``w`` contiguous [T, H*D]; ``state``
+    [slots, H, D, D] (column by column) and ``out`` [T, H*D] 32-bit."""
+    for t in (r, k, v, u, au, w, state, out):
+        if t.dtype != torch.float32:
+            raise KernelError("general_delta_scan: the recurrence is 32-bit")
+    call("fx_general_delta_scan", _ptr(r), _rows(r), _ptr(k), _rows(k), _ptr(v), _rows(v), _ptr(u), _ptr(au), _ptr(w),
+         _ptr(state), _ptr(out), _rows(out), _ptr(token_seq), _ptr(seq_slot), r.shape[0], int(n_entries), int(H), int(D),
          stream if stream is not None else stream_ptr())
     return out
+
+
+def input_conv(x, weight, taps, tail, token_seq, seq_slot, out, update_tail=False, stream=None):
+    """out[t] = x[t] + sum_j weight[:, j] x[t - taps + 1 + j] over the tokens of each request (``weight`` [channels,
+    taps]); the inputs before the step come from ``tail`` [slots, taps - 1, channels] 32-bit.  ``update_tail``: only
+    when every entry brings exactly one token; the kernel then also moves the tail on (:func:`conv_tail_update`
+    otherwise)."""
+    if out.dtype != x.dtype or out.data_ptr() == x.data_ptr():
+        raise KernelError("input_conv: an output of its own, of the input's element type")
+    call("fx_input_conv", _ptr(x), code(x), _rows(x), _ptr(weight), code(weight), int(taps), _ptr(tail), _ptr(token_seq),
+         _ptr(seq_slot), _ptr(out), _rows(out), x.shape[0], x.shape[1], int(update_tail),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def embed_pos(table, ids, pos_table, positions, out, status=None, stream=None):
+    """out[t] = table[ids[t]] + pos_table[positions[t]] in 32 bits."""
+    call("fx_embed_pos", _ptr(table), code(table), _ptr(ids), _ptr(pos_table), code(pos_table), _ptr(positions), _ptr(out),
+         ids.numel(), table.shape[1], table.shape[0], pos_table.shape[0], _ptr(status),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def softcap_(x, cap, stream=None):
+    """x = cap * tanh(x / cap) (32-bit, in place)."""
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("softcap_ takes a contiguous 32-bit tensor")
+    call("fx_softcap", _ptr(x), x.numel(), float(cap), stream if stream is not None else stream_ptr())
+    return x
+
+
+def relu_square_(x, stream=None):
+    """x = max(x, 0)^2 over rows, in place."""
+    call("fx_relu_square", _ptr(x), code(x), _rows(x), x.shape[0], x.shape[1], stream if stream is not None else stream_ptr())
+    return x
 
 
 def rope_table(positions, inv_freq, out, stream=None):
@@ -512,19 +585,20 @@ def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, toke
 
 def paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
                        out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap=None, slopes=None,
-                       stream=None):
+                       stream=None, keep_first=0):
     """:func:`paged_attention` in its general form: keys of ``key_dim`` and values of ``value_dim`` elements whose
     positions lie ``ldk`` / ``ldv`` elements apart in their pages (values that are the leading part of the cached
     key rows: the same tensor twice with ldv = ldk); ``q`` and ``out`` are any tensors addressed by a token stride
     and a head stride; ``slopes`` (float32 [n_heads], optional): slopes[h] * (i - j) is taken off the score of key j
-    for the query at position i."""
+    for the query at position i; ``keep_first`` (with a window): the request's first positions stay visible beside
+    the window."""
     T = positions.numel()
     if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != n_heads):
         raise KernelError("paged_attention_ex: one 32-bit slope per head")
     call("fx_paged_attention_ex", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv), code(q),
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out),
          int(ldo), int(ldoh), T, n_heads, n_kv_heads, key_dim, value_dim, int(window or 0), float(scale),
-         float(softcap or 0.0), _ptr(slopes), stream if stream is not None else stream_ptr())
+         float(softcap or 0.0), _ptr(slopes), int(keep_first or 0), stream if stream is not None else stream_ptr())
     return out
 
 
@@ -574,7 +648,7 @@ def general_attention_items(entries, n_heads: int, n_kv_heads: int):
 
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
                       items, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, slopes=None,
-                      stream=None, n_splits=1, part_o=None, part_ml=None, kv_strides=None):
+                      stream=None, n_splits=1, part_o=None, part_ml=None, kv_strides=None, keep_first=0):
     """:func:`paged_attention_ex` in bfloat16 on the tensor cores (see :func:`general_attention_ok`).  ``items``: the
     device copy of :func:`general_attention_items`, or None when every entry brings one token (a tile a token and
     kv head; nothing comes from the host, so a captured step replays unchanged).  ``n_splits`` > 1 (without items):
@@ -591,24 +665,27 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, pag
     call("fx_general_attention", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv),
          ctypes.cast(strides, c_void_p) if strides is not None else None, _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(items), n, _ptr(out), int(ldo), int(ldoh), n_heads, n_kv_heads, key_dim, value_dim, int(window or 0),
-         float(scale), _ptr(slopes), int(n_splits), _ptr(part_o), _ptr(part_ml),
+         float(scale), _ptr(slopes), int(n_splits), _ptr(part_o), _ptr(part_ml), int(keep_first or 0),
          stream if stream is not None else stream_ptr())
     return out
 
 
 def qk_norm_store(qkv, positions, token_seq, seq_slot, q_weight, k_weight, eps, temperature, k_pages, v_pages, block_table,
-                  page_size, n_heads, n_kv_heads, key_dim, value_dim, write_cache=True, status=None, stream=None):
+                  page_size, n_heads, n_kv_heads, key_dim, value_dim, write_cache=True, status=None, stream=None,
+                  value_norm_eps=None):
     """Rows of [q heads | k heads | v heads] (widths key_dim, key_dim, value_dim), in place: q and k normed per head
     (x / sqrt(mean(x^2) + eps) * weight; weights [key_dim] or None), q times the query temperature
     1 + coef * ln(floor((pos + 1) / every) + 1) (``temperature`` = (coef, every) or None); k and v stored in their
-    pages ([pages, kv heads, page, key_dim] and [.., value_dim])."""
+    pages ([pages, kv heads, page, key_dim] and [.., value_dim]).  ``value_norm_eps``: every value head is divided
+    by its root mean square, v / sqrt(mean(v^2) + eps), on its way into the pages."""
     coef, every = temperature if temperature is not None else (0.0, 0)
     if (q_weight is None) != (k_weight is None):
         raise KernelError("qk_norm_store: both norm weights or none")
     call("fx_qk_norm_store", _ptr(qkv), code(qkv), _rows(qkv), _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(q_weight), _ptr(k_weight), code(q_weight) if q_weight is not None else 0, float(eps), float(coef), int(every),
          _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1], page_size, qkv.shape[0], n_heads,
-         n_kv_heads, key_dim, value_dim, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
+         n_kv_heads, key_dim, value_dim, int(write_cache), _ptr(status),
+         float(value_norm_eps) if value_norm_eps is not None else -1.0, stream if stream is not None else stream_ptr())
 
 
 def latent_prep(q, dkv, positions, token_seq, seq_slot, c_weight, eps, cos_sin, rot_dims, q_plain, q_full, pages,

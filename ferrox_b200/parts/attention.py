@@ -91,13 +91,20 @@ class GqaAttention(Mixer):
         self.qk_norm = getattr(s, "qk_norm", None)
         self.temperature = getattr(s, "query_temperature", None)
         self.slopes_spec = getattr(s, "distance_slopes", None)
-        self.general = bool(self.qk_norm or self.temperature or self.slopes_spec or self.value_dim != s.head_dim)
+        self.value_norm_eps = getattr(s, "value_norm_eps", None)
+        self.keep_first = int(getattr(s, "keep_first", 0) or 0) if s.window is not None else 0
+        self.gate_name = getattr(s, "output_gate", None)
+        if int(getattr(s, "keep_first", 0) or 0) < 0:
+            raise ValueError(f"keep_first={s.keep_first}: a number of positions")
+        self.general = bool(self.qk_norm or self.temperature or self.slopes_spec or self.value_dim != s.head_dim
+                            or self.value_norm_eps is not None or self.keep_first or self.gate_name)
         self.v_size = s.n_kv_heads * self.value_dim
         self.o_size = s.n_heads * self.value_dim
         if self.general:
             if s.position is not None and not isinstance(s.position, NoPositionSpec):
-                raise ValueError("attention with normed queries and keys, a query temperature, a distance bias or its "
-                                 "own value width takes no rotary position encoding")
+                raise ValueError("attention with normed queries, keys or values, a query temperature, a distance bias, "
+                                 "kept first positions, an output gate or its own value width takes no rotary "
+                                 "position encoding")
             if s.tied_values or s.softcap:
                 raise ValueError("the general attention form has neither tied values nor a soft cap")
             if self.slopes_spec is not None and len(self.slopes_spec) != s.n_heads:
@@ -120,8 +127,9 @@ class GqaAttention(Mixer):
         s = self.spec
         if self.value_dim != s.head_dim:
             return CacheSpec(paged=PagedSpec((PagedTensorSpec("k", (s.n_kv_heads, s.head_dim), lead_dims=1),
-                                              PagedTensorSpec("v", (s.n_kv_heads, self.value_dim), lead_dims=1)), s.window))
-        return CacheSpec(paged=KvCacheSpec(s.n_kv_heads, s.head_dim, s.window))
+                                              PagedTensorSpec("v", (s.n_kv_heads, self.value_dim), lead_dims=1)), s.window,
+                                             self.keep_first))
+        return CacheSpec(paged=KvCacheSpec(s.n_kv_heads, s.head_dim, s.window, self.keep_first))
 
     def tensor_decls(self):
         s, n = self.spec, self._names
@@ -134,17 +142,24 @@ class GqaAttention(Mixer):
                   TensorDecl(s.prefix + self.qk_norm[1], (s.head_dim,), init="ones")]
         if s.qkv_bias:
             d += [TensorDecl(n[key + "_bias"], (sizes[key],)) for key in keys]
+        if self.gate_name:
+            d.append(TensorDecl(s.prefix + self.gate_name, (self.o_size, s.hidden)))
         return d
 
     def load(self, src, rt):
         super().load(src, rt)
         n = self._names
         ws = [src.get(n[key]) for key in self._qkv_keys]
+        if self.gate_name:
+            # the output gate reads the same input as q, k and v: its rows follow theirs in the fused product
+            ws.append(src.get(self.spec.prefix + self.gate_name))
         dt = _common_dtype(ws)
         self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.b_qkv = None
         if self.spec.qkv_bias:
             bs = [src.get(n[key + "_bias"]) for key in self._qkv_keys]
+            if self.gate_name:
+                bs.append(torch.zeros(self.o_size, dtype=bs[0].dtype, device=bs[0].device))    # (the gate has no bias)
             bdt = _common_dtype(bs)
             self.b_qkv = torch.cat([b.to(bdt) for b in bs]).contiguous()
         self.w_o = src.get(n["o"])
@@ -247,28 +262,35 @@ class GqaAttention(Mixer):
 
 
     def _forward_general(self, x, out, batch, cache, accumulate):
-        """The form with normed queries and keys, a query temperature, a distance bias, values of their own
-        width: fused [q | k | v] product; one kernel norms q and k per head, applies the temperature and stores k and
-        v; attention with the bias; output product."""
+        """The form with normed queries, keys or values, a query temperature, a distance bias, kept first positions,
+        an output gate, values of their own width: fused [q | k | v (| gate)] product; one kernel norms q and k (and
+        v) per head, applies the temperature and stores k and v; attention with the bias and the mask; the gate;
+        output product."""
         s = self.spec
         T, D, V = x.shape[0], s.head_dim, self.value_dim
-        qkv = self.rt.empty(T, self.q_size + self.kv_size + self.v_size)
+        qkv_width = self.q_size + self.kv_size + self.v_size
+        qkv = self.rt.empty(T, qkv_width + (self.o_size if self.gate_name else 0))
         ops.linear(x, self.w_qkv, qkv, bias=self.b_qkv, status=batch.status, stream=batch.stream, after_short_kernel=True)
         eps = self.qk_norm[2] if self.qk_norm else 0.0
         ops.qk_norm_store(qkv, batch.positions, batch.token_seq, batch.seq_slot, self.q_norm_w, self.k_norm_w, eps,
                           self.temperature, cache.k, cache.v, cache.block_table, cache.page_size, s.n_heads, s.n_kv_heads,
-                          D, V, write_cache=cache.writes, status=batch.status, stream=batch.stream)
+                          D, V, write_cache=cache.writes, status=batch.status, stream=batch.stream,
+                          value_norm_eps=self.value_norm_eps)
         attn = self.rt.empty(T, self.o_size)
         general_attention(qkv, qkv.stride(0), D, cache.k, cache.v, D, V, attn, attn.stride(0), V, batch, cache,
-                          s.n_heads, s.n_kv_heads, D, V, s.window, self.scale, self.slopes, self.rt)
+                          s.n_heads, s.n_kv_heads, D, V, s.window, self.scale, self.slopes, self.rt,
+                          keep_first=self.keep_first)
+        if self.gate_name:
+            ops.gate_heads_(attn, qkv[:, qkv_width:], s.n_heads, stream=batch.stream)
         ops.linear(attn, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream,
                    after_short_kernel=True)
 
 
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, batch, cache, n_heads, n_kv_heads,
-                      key_dim, value_dim, window, scale, slopes, rt):
+                      key_dim, value_dim, window, scale, slopes, rt, keep_first=0):
     """Attention over pages in its general form (keys and values of different widths, strided queries and outputs, an
-    optional distance bias), by the kernel that fits the step: tiles of (token, head) pairs on the tensor cores
+    optional distance bias, a window that may keep the request's first positions visible), by the kernel that fits
+    the step: tiles of (token, head) pairs on the tensor cores
     in bfloat16, a warp per (token, head) on the CUDA cores in 32-bit and for widths that are no multiple of 16."""
     per_sm = ops.general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim)
     if per_sm:
@@ -280,7 +302,7 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, 
             tiles = n_kv_heads * -(-(n_heads // n_kv_heads) // ops.GENERAL_TILE_ROWS)
             reach = cache.block_table.shape[1] * cache.page_size
             if window is not None:
-                reach = min(reach, (window + 63) // 64 * 64 + 64)
+                reach = min(reach, (window + 63) // 64 * 64 + 64 + (keep_first + 63) // 64 * 64)
             _, n_splits = ops.decode_split_plan(T, tiles, reach, per_sm, single_is_final=True)
             if n_splits > 1:
                 part_o = rt.empty(T, n_heads, n_splits, value_dim, dtype=torch.float32)
@@ -295,10 +317,10 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, 
         return ops.general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size,
                                      batch.positions, batch.token_seq, batch.seq_slot, items, out, ldo, ldoh, n_heads,
                                      n_kv_heads, key_dim, value_dim, window, scale, slopes=slopes, stream=batch.stream,
-                                     n_splits=n_splits, part_o=part_o, part_ml=part_ml)
+                                     n_splits=n_splits, part_o=part_o, part_ml=part_ml, keep_first=keep_first)
     ops.paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size, batch.positions,
                            batch.token_seq, batch.seq_slot, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim,
-                           window, scale, slopes=slopes, stream=batch.stream)
+                           window, scale, slopes=slopes, stream=batch.stream, keep_first=keep_first)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)

@@ -19,26 +19,33 @@ class PreNormBlock(Block):
         super().__init__(spec)
         self.norm1 = build_part(spec.norm1)
         self.mixer = build_part(spec.mixer)
-        self.norm2 = build_part(spec.norm2)
-        self.ffn = build_part(spec.ffn)
+        # (a layer without a feed-forward ends after its mixer and has no second norm)
+        self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        self.norm2 = build_part(spec.norm2) if self.ffn is not None else None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
     def tensor_decls(self):
-        return (
-            self.norm1.tensor_decls() + self.mixer.tensor_decls() + self.norm2.tensor_decls() + self.ffn.tensor_decls()
-        )
+        from ..weights.loader import TensorDecl
+
+        d = [x for p in self._parts() for x in p.tensor_decls()]
+        # tensors a checkpoint may hold for this layer although nothing reads them
+        d += [TensorDecl(n, tuple(shape), optional=True) for n, shape in getattr(self.spec, "unused_tensors", ())]
+        return d
 
     def load(self, src, rt):
         super().load(src, rt)
-        for part in (self.norm1, self.mixer, self.norm2, self.ffn):
+        for part in self._parts():
             part.load(src, rt)
 
     def reset_after_fault(self):
-        for part in (self.norm1, self.mixer, self.norm2, self.ffn):
+        for part in self._parts():
             part.reset_after_fault()
 
     @property
     def graph_safe(self):
-        return all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.ffn))
+        return all(p.graph_safe for p in self._parts())
 
     passes_norm = True
 
@@ -50,6 +57,8 @@ class PreNormBlock(Block):
                 x = self.norm1.forward(h)
         with ops.trace_scope("mixer"):
             self.mixer.forward_add(x, h, batch, cache)
+        if self.ffn is None:
+            return None
         with ops.trace_scope("norm"):
             x2 = self.norm2.forward(h)
         with ops.trace_scope("feed-forward"):

@@ -11,6 +11,13 @@ gated by SiLU(Wg x) before the output projection.  The convolution's last taps -
 ``decayed_linear_attention``:  S <- d_h S + k v^T, o = S^T q on SiLU(q, k, v) with one fixed decay per head; the
 heads' read-outs are RMS-normed together, weighted, and gated by sigmoid(Wg x).
 
+``general_delta_rule``:  per head a state S [head_dim, head_dim] with a decay w and a removal rate a per key channel,
+
+    u = k / sqrt(sum k^2 + 1e-6);   S <- diag(w) S - (a u) (u^T S) + k v^T;   o = S^T r
+
+(both terms read the state of the token before), w = exp(-rate sigmoid(W2 tanh(W1 x) + w0)), a = sigmoid(Wa x + ba);
+each head's o is RMS-normed, the concatenated heads weighted and gated by sigmoid(Wg x).
+
 The states live in the cache manager's slots as 32-bit tensors; the recurrences, the gates and the norms are
 32-bit (``csrc/linear_state.cu``); the projections run in the engine's dtype.  Tokens of a request are taken in
 order whatever the step looks like, so a position's output does not depend on how the request was cut.
@@ -155,5 +162,60 @@ class DecayedLinearAttention(_StateMixer):
         ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
 
 
+class GeneralDeltaRule(_StateMixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if s.head_dim > 256:
+            raise ValueError(f"head_dim={s.head_dim}: the recurrence kernel holds at most 256 rows of a state column")
+        if s.decay_rank < 1:
+            raise ValueError(f"decay_rank={s.decay_rank}: the decay's inner width is positive")
+        self.hd = s.n_heads * s.head_dim
+
+    def cache_spec(self):
+        s = self.spec
+        return CacheSpec(state=StateSpec(parts=(("matrix", (s.n_heads, s.head_dim, s.head_dim)),)))   # column by column
+
+    def tensor_decls(self):
+        s, p, hd = self.spec, self.spec.prefix, self.hd
+        d = [TensorDecl(p + n, (hd, s.hidden)) for n in ("r", "k", "v", "g", "a")]
+        d += [
+            TensorDecl(p + "a.b", (hd,)), TensorDecl(p + "w1", (s.decay_rank, s.hidden)),
+            TensorDecl(p + "w2", (hd, s.decay_rank)), TensorDecl(p + "w0", (hd,)),
+            TensorDecl(p + "norm", (hd,), init="ones"), TensorDecl(p + "o", (s.hidden, hd)),
+        ]
+        return d
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        p = self.spec.prefix
+        # one product for everything the mixer reads from its input: rows [r | k | v | gate | a | w1]; its output is
+        # written in 32 bits, because all but the gate enters the recurrence
+        self.w_in = _cat_rows([src.get(p + n) for n in ("r", "k", "v", "g", "a", "w1")])
+        self.w2 = src.get(p + "w2")
+        self.w0 = src.get(p + "w0")
+        self.a_bias = src.get(p + "a.b")
+        self.norm_w = src.get(p + "norm")
+        self.w_o = src.get(p + "o")
+
+    def forward_into(self, x, out, batch, cache, accumulate=False):
+        s, rt = self.spec, self.rt
+        T, H, D, hd = x.shape[0], s.n_heads, s.head_dim, self.hd
+        f32 = torch.float32
+        proj = rt.empty(T, 5 * hd + s.decay_rank, dtype=f32)
+        ops.linear(x, self.w_in, proj, status=batch.status, stream=batch.stream)
+        r, k, v, gate = (proj[:, i * hd:(i + 1) * hd] for i in range(4))
+        u, au, w = rt.empty(T, hd, dtype=f32), rt.empty(T, hd, dtype=f32), rt.empty(T, hd, dtype=f32)
+        ops.general_delta_prep(k, proj[:, 4 * hd:5 * hd], proj[:, 5 * hd:], self.w2, self.w0, self.a_bias, s.decay_rate,
+                               u, au, w, H, D, stream=batch.stream)
+        read = rt.empty(T, hd, dtype=f32)
+        ops.general_delta_scan(r, k, v, u, au, w, cache.states["matrix"], read, batch.token_seq, batch.seq_slot,
+                               batch.n_seqs, H, D, stream=batch.stream)
+        y = rt.empty(T, hd)
+        ops.gated_group_norm(read, gate, self.norm_w, s.norm_eps, "sigmoid", y, H, D, stream=batch.stream)
+        ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
+
+
 register_part("gated_delta_rule", GatedDeltaRule, replace=True)
+register_part("general_delta_rule", GeneralDeltaRule, replace=True)
 register_part("decayed_linear_attention", DecayedLinearAttention, replace=True)

@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward: down( silu(gate x) * (up x) ), no bias
+"""Dense feed-forwards.  SwiGLU: down( silu(gate x) * (up x) ), no bias; plain: down( relu(up x)^2 )
 (reference: crates/ferrox-moe/src/lib.rs:655-658; decoder.rs:2902-2913)."""
 from __future__ import annotations
 
@@ -51,4 +51,38 @@ class SwigluMlp(FeedForward):
         ops.linear(act, self.w_down, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
 
 
+class PlainMlp(FeedForward):
+    """down(act(up x)) without a gate; act = the square of ReLU.  The activation runs on the rows the first product
+    wrote, in place."""
+
+    graph_safe = True
+    ACTIVATIONS = ("relu_square",)
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        if spec.activation not in self.ACTIVATIONS:
+            raise ValueError(f"plain_mlp activation {spec.activation!r}: known: {', '.join(self.ACTIVATIONS)}")
+        names = getattr(spec, "tensor_names", None) or ("up", "down")
+        self._up, self._down = (spec.prefix + n for n in names)
+
+    def tensor_decls(self):
+        s = self.spec
+        return [TensorDecl(self._up, (s.intermediate, s.hidden)), TensorDecl(self._down, (s.hidden, s.intermediate))]
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        self.w_up = src.get(self._up)
+        self.w_down = src.get(self._down)
+
+    def forward_add(self, x, h, batch):
+        self.forward_into(x, h, batch, accumulate=True)
+
+    def forward_into(self, x, out, batch, accumulate=False):
+        act = self.rt.empty(x.shape[0], self.spec.intermediate)
+        ops.linear(x, self.w_up, act, status=batch.status, stream=batch.stream)
+        ops.relu_square_(act, stream=batch.stream)
+        ops.linear(act, self.w_down, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
+
+
 register_part("swiglu_mlp", SwigluMlp, replace=True)
+register_part("plain_mlp", PlainMlp, replace=True)

@@ -48,6 +48,8 @@ class DecoderModel(Part):
     def tensor_decls(self) -> List[TensorDecl]:
         s = self.spec
         d = [TensorDecl(s.embedding_name, (s.vocab_size, s.hidden))]
+        if getattr(s, "position_table", None):
+            d.append(TensorDecl(s.position_table, (s.max_positions, s.hidden)))
         if self.embedding_norm is not None:
             d += self.embedding_norm.tensor_decls()
         for layer in self.layers:
@@ -61,6 +63,7 @@ class DecoderModel(Part):
         super().load(src, rt)
         s = self.spec
         self.embedding = src.get(s.embedding_name)
+        self.position_table = src.get(s.position_table) if getattr(s, "position_table", None) else None
         for layer in self.layers:
             layer.load(src, rt)
         self.final_norm.load(src, rt)
@@ -101,7 +104,12 @@ class DecoderModel(Part):
         s, rt = self.spec, self.rt
         h = rt.empty(batch.n_tokens, s.hidden, dtype=torch.float32)
         with ops.trace_scope("embedding"):
-            ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
+            if self.position_table is not None:
+                # a learned position vector is added to every embedding row, in 32 bits
+                ops.embed_pos(self.embedding, batch.token_ids, self.position_table, batch.positions, h,
+                              status=batch.status, stream=batch.stream)
+            else:
+                ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
             if self.embedding_norm is not None:
                 self.embedding_norm.forward_in_place(h)
         x = None    # the next block's first norm of h, when the block before it has computed it
@@ -122,4 +130,6 @@ class DecoderModel(Part):
             ops.linear(x, self.head, logits, status=batch.status, stream=batch.stream)
             if s.logit_scale != 1.0:
                 ops.scale_(logits, s.logit_scale, stream=batch.stream)
+            if getattr(s, "logit_softcap", None):
+                ops.softcap_(logits, s.logit_softcap, stream=batch.stream)
         return logits

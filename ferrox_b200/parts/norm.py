@@ -39,29 +39,37 @@ class RmsNorm(Norm):
 
 
 class LayerNorm(Norm):
-    """(x - mean) / sqrt(variance + eps) * w, the variance being the mean of the squared deviations; a weight and
-    no bias; statistics in 32 bits."""
+    """(x - mean) / sqrt(variance + eps) * w (+ b), the variance being the mean of the squared deviations; a weight
+    and, where the spec names one, a bias; statistics in 32 bits."""
 
     graph_safe = True
 
+    def _bias_name(self):
+        return getattr(self.spec, "bias_name", None)
+
     def tensor_decls(self):
-        return [TensorDecl(self.spec.name, (self.spec.size,), init="ones")]
+        d = [TensorDecl(self.spec.name, (self.spec.size,), init="ones")]
+        if self._bias_name():
+            d.append(TensorDecl(self._bias_name(), (self.spec.size,)))
+        return d
 
     def load(self, src, rt):
         super().load(src, rt)
         self.weight = src.get(self.spec.name)
+        self.bias = src.get(self._bias_name()) if self._bias_name() else None
 
     def forward(self, h, rows=None):
         n = h.shape[0] if rows is None else rows.numel()
         out = self.rt.empty(n, self.spec.size)
-        return ops.layernorm(h, self.weight, self.spec.eps, out, rows=rows)
+        return ops.layernorm(h, self.weight, self.spec.eps, out, rows=rows, bias=self.bias)
 
     def forward_in_place(self, h):
         """The 32-bit stream normed where it lies."""
-        return ops.layernorm(h, self.weight, self.spec.eps, h)
+        return ops.layernorm(h, self.weight, self.spec.eps, h, bias=self.bias)
 
     def as_layer_norm(self):
-        return self.weight, self.spec.eps
+        """(weight, eps) for a kernel that applies the norm itself; None with a bias, which those kernels lack."""
+        return (self.weight, self.spec.eps) if self.bias is None else None
 
 
 register_part("rms_norm", RmsNorm, replace=True)

@@ -30,12 +30,13 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class LayerNormSpec:
-    """(x - mean) / sqrt(variance + eps) * w over whole rows; a weight and no bias."""
+    """(x - mean) / sqrt(variance + eps) * w (+ b) over whole rows; a weight and, with ``bias_name``, a bias."""
 
     size: int
     eps: float
     name: str  # the weight tensor's full name
     kind: str = "layer_norm"
+    bias_name: Optional[str] = None  # the bias tensor's full name (None: no bias)
 
 
 @dataclass(frozen=True)
@@ -89,6 +90,13 @@ class AttentionSpec:
     query_temperature: Optional[Tuple[float, int]] = None
     # one slope per head: slope * (i - j) is taken off the score of key j for the query at position i
     distance_slopes: Optional[Tuple[float, ...]] = None
+    # every value head is divided by its root mean square, v / sqrt(mean(v^2) + eps), without a weight, and cached so
+    value_norm_eps: Optional[float] = None
+    # with a window: the first keep_first positions of a request stay visible beside the window
+    keep_first: int = 0
+    # name (after <prefix>) of a [n_heads * value_dim, hidden] matrix g: the concatenated heads are multiplied
+    # element by element with sigmoid(g x) before the output projection
+    output_gate: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -134,6 +142,38 @@ class GatedDeltaSpec:
 
 
 @dataclass(frozen=True)
+class GeneralDeltaSpec:
+    """Generalized delta rule: per head a [head_dim, head_dim] state S with a decay and a removal rate per key
+    channel, S = diag(w) S - (a u)(u^T S) + k v^T with the unit key u, o = S^T r;
+    w = exp(-decay_rate sigmoid(w2 tanh(w1 x) + w0)), a = sigmoid(a x + a.b); each head's o is RMS-normed, the
+    concatenated heads are weighted by ``norm`` and gated by sigmoid(g x).
+    Tensors: <prefix>{r,k,v,g,a,o}, <prefix>a.b, <prefix>w1 [rank, hidden], <prefix>w2 [H*D, rank], <prefix>w0,
+    <prefix>norm [H*D]."""
+
+    hidden: int
+    n_heads: int
+    head_dim: int
+    decay_rank: int
+    decay_rate: float
+    norm_eps: float
+    prefix: str
+    kind: str = "general_delta_rule"
+
+
+@dataclass(frozen=True)
+class InputConvSpec:
+    """A mixer that reads x + conv(x) instead of x: a causal convolution over time on every channel,
+    conv(x)_t = sum_j w[:, j] x_(t - taps + 1 + j), zeros before the request's start; ``name``: the [channels, taps]
+    weight tensor's full name.  The last taps - 1 inputs are part of the request's state."""
+
+    mixer: object
+    channels: int
+    taps: int
+    name: str
+    kind: str = "input_conv"
+
+
+@dataclass(frozen=True)
 class DecayedLinearAttentionSpec:
     """Linear attention with one fixed decay per head: S = d S + k v^T, o = S^T q on SiLU(q, k, v); the heads'
     read-outs are RMS-normed together and gated by a sigmoid.  Tensors: <prefix>{q,k,v,g,o}, <prefix>norm."""
@@ -168,6 +208,19 @@ class DenseMlpSpec:
 
 
 @dataclass(frozen=True)
+class PlainMlpSpec:
+    """down(act(up x)) without a gate; act: relu_square (max(z, 0)^2).  Tensors <prefix>{up,down} unless
+    ``tensor_names`` spells them differently."""
+
+    hidden: int
+    intermediate: int
+    prefix: str
+    activation: str = "relu_square"
+    tensor_names: Optional[Tuple[str, str]] = None
+    kind: str = "plain_mlp"
+
+
+@dataclass(frozen=True)
 class MoeSpec:
     hidden: int
     n_experts: int
@@ -191,13 +244,15 @@ class MoeSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """h += mixer(norm1(h)); h += ffn(norm2(h))."""
+    """h += mixer(norm1(h)); h += ffn(norm2(h)).  ``ffn`` None: the layer ends after the mixer (and has no norm2);
+    ``unused_tensors``: (name, shape) of tensors a checkpoint may carry for the layer all the same."""
 
     norm1: object
     mixer: object
-    norm2: object
-    ffn: object
+    norm2: Optional[object]
+    ffn: Optional[object]
     kind: str = "pre_norm"
+    unused_tensors: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
 
 @dataclass(frozen=True)
@@ -252,6 +307,8 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = field(default_factory=tuple)
     embedding_norm: Optional[object] = None  # a norm applied to the embedding rows (the stream stays 32-bit)
     logit_scale: float = 1.0  # the head's output is multiplied by this
+    position_table: Optional[str] = None  # a learned [max_positions, hidden] table: row p is added to position p's embedding
+    logit_softcap: Optional[float] = None  # c: the logits pass through c * tanh(z / c)
 
     @property
     def n_caches(self) -> int:

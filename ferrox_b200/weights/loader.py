@@ -100,6 +100,15 @@ class WeightSource:
         return t.to(self.device).to(want).contiguous()
 
 
+def folder_shapes(folder: str) -> Dict[str, Tuple[int, ...]]:
+    """name -> shape of every tensor a model folder holds (headers only), for designs that leave a size to them."""
+    files = ModelFiles(folder)
+    try:
+        return {n: tuple(files.info(n)[1]) for n in files.names()}
+    finally:
+        files.close()
+
+
 def open_folder(folder: str, decls: Sequence[TensorDecl], device, compute_dtype) -> Tuple[WeightSource, ModelFiles]:
     files = ModelFiles(folder)
     check_declared({n: files.info(n)[1] for n in files.names()}, decls, folder)
