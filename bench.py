@@ -215,6 +215,26 @@ def moe_like(width, layers, vocab=32768):
                 vocab_size=vocab, max_position_embeddings=CONTEXT)
 
 
+def sesuzen_shape(width, layers, ff, vocab=32768, window=1024, moe=False):
+    """Layer sizes that resemble a real model's: generalized-delta layers with heads of 64 (a state of 64 x 64 a head,
+    a decay of inner width 64) and attention layers with heads of 128 on a quarter as many key heads, a window of
+    1,024 that keeps the first 4 positions, in turn; four taps of input convolution.  The mixers hold 4.75 x width^2
+    parameters a layer on average against 5.625 x width^2 in the Safepel shape; the difference goes into the dense
+    feed-forward.  ``moe``: 60 experts of which a token uses 4 instead, as wide as the Qwen2-MoE shape's."""
+    h = width // 128
+    if moe:
+        mlp = {"kind": "moe", "expert": {"ff": width * 11 // 16 // 64 * 64}, "router": {"experts": 60, "top": 4}}
+    else:
+        mlp = {"kind": "dense", "ff": (ff + 7 * width // 16 + 63) // 64 * 64}
+    delta = {"type": "general_delta", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "mlp": mlp}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+        "mask": {"size": window, "keep_first": 4}}}
+    return {"architecture": "Sesuzen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "max_positions": CONTEXT, "logit_softcap": 30.0,
+            "layers": [delta if i % 2 == 0 else att for i in range(layers)]}
+
+
 def compare_designs(args) -> int:
     """Prefill and decode throughput of a design and of the closest existing decoder at a few equal sizes (random
     bfloat16 weights), with the device time of every class of kernel from a traced pass beside them."""
@@ -314,6 +334,24 @@ def compare_designs(args) -> int:
 
     pk = peaks()
     rows = []
+    if args.designs in ("sesuzen", "sesuzen-moe"):
+        moe = args.designs == "sesuzen-moe"
+        for width, layers, ff in sizes:
+            a = sesuzen_shape(width, layers, ff, moe=moe)
+            if moe:
+                b = dict(moe_like(width, layers), shared_expert_intermediate_size=0)
+                row = {"width": width, "layers": layers, "expert_ff": b["moe_intermediate_size"]}
+            else:
+                b = safepel_shape(width, layers, ff)
+                row = {"width": width, "layers": layers, "ff": a["layers"][0]["mlp"]["ff"], "safepel_ff": ff}
+            row["sesuzen"] = measure(a)
+            row["qwen2_moe" if moe else "safepel"] = measure(b)
+            rows.append(row)
+        beside = "the Qwen2-MoE decoder (no shared expert)" if moe else "Safepel"
+        print(json.dumps({"designs": f"Sesuzen beside {beside} at equal size", "dtype": "bf16", "batch": batch,
+                          "prompt_tokens": PREFILL_TOKENS, "decode_steps_timed": steps, "peaks": pk,
+                          "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "sizes": rows}))
+        return 0
     if args.designs == "bobepel":
         for width, layers, _ in sizes:
             a, b = bobepel_shape(width, layers), moe_like(width, layers)
@@ -346,10 +384,11 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps each; the median counts")
-    ap.add_argument("--designs", nargs="?", const="safepel", default=None, choices=["safepel", "bobepel"],
+    ap.add_argument("--designs", nargs="?", const="safepel", default=None, choices=["safepel", "bobepel", "sesuzen", "sesuzen-moe"],
                     help="instead of the default workload: prefill and decode of a design beside the closest existing "
                          "decoder at a few equal sizes, with device time per class of kernel (safepel: beside the dense "
-                         "Qwen2 decoder; bobepel: beside the Qwen2-MoE decoder)")
+                         "Qwen2 decoder; bobepel: beside the Qwen2-MoE decoder; sesuzen: dense feed-forwards, beside "
+                         "Safepel; sesuzen-moe: experts, beside the Qwen2-MoE decoder without its shared expert)")
     ap.add_argument("--widths", default="", help="--designs: only these widths (commas), e.g. 2048")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -6,9 +6,26 @@ or 64-bit where a test wants a reference that rounding does not reach).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
+
+_round = lambda t: t
+
+
+@contextlib.contextmanager
+def rounded_to(dtype):
+    """Within the block, everything that the design allows in reduced precision (the inputs and outputs of matrix
+    products, activations between them) is rounded to ``dtype`` and back; what it wants in 32-bit is not.  The
+    distance of such a run from the exact one is what rounding alone costs a model: the measure for an engine that
+    computes in ``dtype``."""
+    global _round
+    old, _round = _round, (lambda t: t.to(dtype).to(t.dtype))
+    try:
+        yield
+    finally:
+        _round = old
 
 
 def layer_norm(x, w, b, eps):
@@ -51,10 +68,10 @@ def mixer_attention(x, m, W, p, eps):
     n = x.shape[0]
     H, D = m["heads"], m["dim"]
     G, V = m.get("kv_heads", H), m.get("vdim", D)
-    q = (x @ W[p + "q"].T + W[p + "q.b"]).view(n, H, D)
-    k = (x @ W[p + "k"].T + W[p + "k.b"]).view(n, G, D)
-    v = (x @ W[p + "v"].T + W[p + "v.b"]).view(n, G, V)
-    v = unit_rms(v, eps)
+    q = _round(x @ W[p + "q"].T + W[p + "q.b"]).view(n, H, D)
+    k = _round(x @ W[p + "k"].T + W[p + "k.b"]).view(n, G, D)
+    v = _round(x @ W[p + "v"].T + W[p + "v.b"]).view(n, G, V)
+    v = _round(unit_rms(v, eps))
     rep = H // G
     kk = k.repeat_interleave(rep, dim=1)
     vv = v.repeat_interleave(rep, dim=1)
@@ -63,8 +80,8 @@ def mixer_attention(x, m, W, p, eps):
     ok = visible(n, mask["size"], mask.get("keep_first", 0)) if mask else visible(n)
     s = s.masked_fill(~ok[None], float("-inf"))
     a = torch.softmax(s, dim=-1)
-    o = torch.einsum("hij,jhd->ihd", a, vv).reshape(n, H * V)
-    o = o * torch.sigmoid(x @ W[p + "g"].T)
+    o = _round(torch.einsum("hij,jhd->ihd", a, vv).reshape(n, H * V))
+    o = _round(o * torch.sigmoid(_round(x @ W[p + "g"].T)))
     return o @ W[p + "o"].T
 
 
@@ -104,13 +121,13 @@ def mixer_general_delta(x, m, W, p, eps):
     r, k, v, w, a = delta_inputs(x, m, W, p)
     o, _ = delta_recurrence(r, k, v, w, a)
     o = unit_rms(o, eps).reshape(n, -1) * W[p + "norm"]
-    o = o * torch.sigmoid(x @ W[p + "g"].T)
+    o = _round(o * torch.sigmoid(x @ W[p + "g"].T))
     return o @ W[p + "o"].T
 
 
 def ffn_dense(x, W, p):
-    z = torch.relu(x @ W[p + "up"].T)
-    return (z * z) @ W[p + "down"].T
+    z = torch.relu(_round(x @ W[p + "up"].T))
+    return _round(z * z) @ W[p + "down"].T
 
 
 def route(x, f, W, p):
@@ -131,7 +148,7 @@ def ffn_moe(x, f, W, p, chosen=None):
             continue
         xe = x[rows]
         g = xe @ W[p + f"e{e}.gate"].T
-        y = (g * torch.sigmoid(g) * (xe @ W[p + f"e{e}.up"].T)) @ W[p + f"e{e}.down"].T
+        y = _round(g * torch.sigmoid(g) * (xe @ W[p + f"e{e}.up"].T)) @ W[p + f"e{e}.down"].T
         out[rows] += y * (wt * hit)[rows].sum(dim=-1, keepdim=True)
     return out
 
@@ -148,8 +165,8 @@ def layer_runs(cfg):
 
 def run_layer(h, i, cfg, W, margins=None):
     layer, eps, p = cfg["layers"][i], cfg["norm"]["eps"], f"l{i}."
-    x = layer_norm(h, W[p + "norm1"], W[p + "norm1.b"], eps)
-    x = input_convolution(x, W[p + "canon1"])
+    x = _round(layer_norm(h, W[p + "norm1"], W[p + "norm1.b"], eps))
+    x = _round(input_convolution(x, W[p + "canon1"]))
     if layer["type"] == "attention":
         h = h + mixer_attention(x, layer["mixer"], W, p + "mix.", eps)
     elif layer["type"] == "general_delta":
@@ -159,7 +176,7 @@ def run_layer(h, i, cfg, W, margins=None):
     f = layer.get("mlp")
     if f is None:
         return h
-    x = layer_norm(h, W[p + "norm2"], W[p + "norm2.b"], eps)
+    x = _round(layer_norm(h, W[p + "norm2"], W[p + "norm2.b"], eps))
     if f["kind"] == "dense":
         return h + ffn_dense(x, W, p + "mlp.")
     if margins is not None:
@@ -181,7 +198,7 @@ def forward(cfg, W, tokens, return_layers=False, return_margins=False):
     for i in layer_runs(cfg):
         h = run_layer(h, i, cfg, W, margins if return_margins else None)
         streams.append(h)
-    x = layer_norm(h, W["final.norm"], W["final.norm.b"], cfg["norm"]["eps"])
+    x = _round(layer_norm(h, W["final.norm"], W["final.norm.b"], cfg["norm"]["eps"]))
     z = x @ W["embed"].T
     cap = cfg.get("logit_softcap")
     if cap:
