@@ -36,6 +36,13 @@ __device__ __forceinline__ float load_any(const void* p, int dtype, long i) {
                            : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
 }
 
+// What a plain product's result may pass through before it is stored (the kernels' `gated` argument below zero:
+// -code): 1 the square of ReLU.
+__device__ __forceinline__ float fx_unary(float x, int code) {
+    if (code == 1) { x = fmaxf(x, 0.f); x *= x; }
+    return x;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -100,6 +107,13 @@ __device__ __forceinline__ void fx_pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+
+// The two halves apart, for a kernel that runs long on few warps (a recurrence over a prompt's tokens): blocks of the
+// kernel after it that were set up early wait on the same SMs and take issue slots from it (a prompt of 2,048 tokens
+// through a delta-rule recurrence on a B200: 1.39 ms beside waiting blocks, 0.65 ms alone).  Such a kernel waits first
+// thing and lets its dependents start when its long loop is over.
+__device__ __forceinline__ void fx_pdl_wait_only() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void fx_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // fx_set_pdl(0) (elementwise.cu) makes fx_launch_pdl launch without the attribute; for measurements.
 extern int g_fx_pdl_enabled;

@@ -203,6 +203,7 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                 if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
                 if (MODE == 1) v = a.act == 2 ? fx_clamped_glu<false>(v, up, a.act_limit, a.act_alpha)
                                                : (a.act ? fmaxf(v, 0.f) : v / (1.0f + expf(-v))) * up;
+                else if (a.act) v = fx_unary(v, a.act);     // a plain product with an activation on its result
                 auto store = [&](int col, float val) {
                     const long at = a.c_transposed ? (long)col * a.ldc + r : (long)r * a.ldc + col;
                     if (a.c_dtype == FX_F32) {
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                 store(n, v);
                 if (MODE == 2 && n + 16 < a.N) {
                     if (a.bias) up += load_any(a.bias, a.bias_dtype, n + 16);
+                    if (a.act) up = fx_unary(up, a.act);
                     store(n + 16, up);
                 }
             }
@@ -245,6 +247,9 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
                               const int* group_offsets, const int* active_groups, int n_slots, int tokens_hint,
                               int c_transposed, void* stream)
 {
+    // gated < 0: a plain product whose result passes through the activation -gated (fx_unary) before it is stored
+    const int unary = gated < 0 ? -gated : 0;
+    if (gated < 0) gated = 0;
     if (n_tokens <= 0 || N <= 0) return FX_OK;
     if (K % 32 != 0 || K <= 0) return FX_ERR_SIZE;
     if (ldw % 8 || ldx % 8 || w_group_stride % 8 || (uintptr_t)W % 16 || (uintptr_t)X % 16) return FX_ERR_ALIGN;
@@ -254,7 +259,7 @@ extern "C" int fx_gemm_skinny(const void* X, long ldx, const int* x_rows, const 
     a.X = (const bf16*)X; a.ldx = ldx; a.x_rows = x_rows;
     a.bias = bias; a.bias_dtype = bias_dtype;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate; a.c_transposed = c_transposed;
-    a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha;
+    a.n_tokens = n_tokens; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : unary; a.act_limit = act_limit; a.act_alpha = act_alpha;
     a.group_offsets = group_offsets; a.active_groups = active_groups; a.n_slots = n_slots;
     // grouped: one block row per expert slot (many short blocks hide each other's start-up better than
     // few long ones; measured)

@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                     if (a.bias) x += bias_s[quad][c * 32 + j];
                     if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
                                            : (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
+                    else if (a.act) x = fx_unary(x, a.act);     // a plain product with an activation on its result
                     v[j] = x;
                 }
                 if (fast) {
@@ -408,6 +409,9 @@ extern "C" int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long
                           const int* group_offsets, int n_groups,
                           int* status, void* stream)
 {
+    // gated < 0: a plain product whose result passes through the activation -gated (fx_unary) before it is stored
+    const int unary = gated < 0 ? -gated : 0;
+    if (gated < 0) gated = 0;
     if (M <= 0 || N <= 0) return FX_OK;
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
     if (ldx % 8 || ldw % 8 || w_group_stride % 8 || (uintptr_t)X % 16 || (uintptr_t)W % 16) return FX_ERR_ALIGN;
@@ -416,7 +420,7 @@ extern "C" int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long
     TcArgs a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : unary; a.act_limit = act_limit; a.act_alpha = act_alpha;
     a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     // wide outputs take 128 x 256 tiles (fewer bytes fetched per flop; measured faster even when they give

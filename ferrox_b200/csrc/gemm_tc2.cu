@@ -243,6 +243,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc2_kernel(const __grid_cons
                     if (a.bias) x += bias_s[quad][c * 32 + j];
                     if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
                                            : (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
+                    else if (a.act) x = fx_unary(x, a.act);     // a plain product with an activation on its result
                     v[j] = x;
                 }
                 if (fast) {
@@ -335,6 +336,9 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
                            void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
                            int gate_up_offset, float act_limit, float act_alpha, int* status, void* stream)
 {
+    // gated < 0: a plain product whose result passes through the activation -gated (fx_unary) before it is stored
+    const int unary = gated < 0 ? -gated : 0;
+    if (gated < 0) gated = 0;
     if (M <= 0 || N <= 0) return FX_OK;
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
     if (ldx % 8 || ldw % 8 || (uintptr_t)X % 16 || (uintptr_t)W % 16) return FX_ERR_ALIGN;
@@ -342,7 +346,7 @@ extern "C" int fx_gemm_tc2(const void* X, long ldx, const void* W, long ldw, int
     Tc2Args a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.gated = gated; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha; a.status = status;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.gated = gated; a.act = gated > 0 ? gated - 1 : unary; a.act_limit = act_limit; a.act_alpha = act_alpha; a.status = status;
     CUtensorMap ma, mb;
     if (!make_map(&ma, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BM)) return FX_ERR_SIZE;
     if (!make_map(&mb, W, (uint64_t)K, (uint64_t)w_rows, (uint64_t)ldw, BNH)) return FX_ERR_SIZE;

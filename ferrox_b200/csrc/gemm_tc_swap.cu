@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                     float x = __uint_as_float(r[j]) + bias;
                     if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
                                            : (a.act ? fmaxf(x, 0.f) : x / (1.0f + __expf(-x))) * __uint_as_float(u[j]);
+                    else if (a.act) x = fx_unary(x, a.act);     // a plain product with an activation on its result
                     if (a.k_splits > 1) {   // a run of K: the plain partial sum
                         a.partials[((long)t.split * a.M + row0 + j) * a.N + f] = __uint_as_float(r[j]);
                         continue;
@@ -394,6 +395,9 @@ extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw,
                                int tokens_per_tile, int weights_first, int k_splits, float* partials, int* status,
                                void* stream)
 {
+    // gated < 0: a plain product whose result passes through the activation -gated (fx_unary) before it is stored
+    const int unary = gated < 0 ? -gated : 0;
+    if (gated < 0) gated = 0;
     if (M <= 0 || N <= 0) return FX_OK;
     if (K <= 0 || K % 8) return FX_ERR_SIZE;
     if (ldx % 8 || ldw % 8 || w_group_stride % 8 || (uintptr_t)X % 16 || (uintptr_t)W % 16) return FX_ERR_ALIGN;
@@ -402,10 +406,10 @@ extern "C" int fx_gemm_tc_swap(const void* X, long ldx, const void* W, long ldw,
     SwArgs a;
     a.C = C; a.ldc = ldc; a.c_dtype = c_dtype; a.accumulate = accumulate;
     a.bias = bias; a.bias_dtype = bias_dtype;
-    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : 0; a.act_limit = act_limit; a.act_alpha = act_alpha;
+    a.M = M; a.N = N; a.K = K; a.gate_up_offset = gate_up_offset; a.act = gated > 0 ? gated - 1 : unary; a.act_limit = act_limit; a.act_alpha = act_alpha;
     a.group_offsets = group_offsets; a.n_groups = n_groups; a.status = status; a.weights_first = weights_first;
     a.k_splits = k_splits > 1 ? k_splits : 1; a.partials = partials;
-    if (a.k_splits > 1 && (group_offsets || gated || !partials || a.k_splits > (K + BK - 1) / BK)) return FX_ERR_SIZE;
+    if (a.k_splits > 1 && (group_offsets || gated || unary || !partials || a.k_splits > (K + BK - 1) / BK)) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     int tnb = tokens_per_tile;
     if (tnb == 0) tnb = group_offsets ? 128 : (M <= 32 ? 32 : M <= 64 ? 64 : 128);

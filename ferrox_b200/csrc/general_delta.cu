@@ -35,33 +35,99 @@ __device__ __forceinline__ int first_row_of(const int* __restrict__ token_seq, i
     return lo;
 }
 
-__global__ void general_delta_prep_kernel(
+constexpr int GP_THREADS = 128;
+constexpr int GP_RC = 64;           // low-rank channels a pass
+constexpr int GP_MAX_TT = 8;        // tokens a block
+constexpr int GP_ITEMS = GP_MAX_TT * 256 / GP_THREADS;
+
+// One block: `tt_n` tokens of one head.  The head's rows of W2 pass through shared memory GP_RC columns at a time
+// (read along their rows, so the loads coalesce, and kept with an odd stride, so the threads of a warp, one key
+// channel each, meet no bank twice); every (token, channel) sums its products in the order of the low-rank index,
+// whatever the block holds beside it.
+__global__ void __launch_bounds__(GP_THREADS) general_delta_prep_kernel(
     const float* __restrict__ k, long ldk, const float* __restrict__ a_pre, long lda, const float* __restrict__ w1_out,
     long ldw1, const void* __restrict__ w2, int w2_dtype, const void* __restrict__ w0, int w0_dtype,
     const void* __restrict__ a_bias, int ab_dtype, float rate, float* __restrict__ u, float* __restrict__ au,
-    float* __restrict__ w, int H, int D, int rank)
+    float* __restrict__ w, int n_tokens, int H, int D, int rank, int tt_n)
 {
-    extern __shared__ float th_s[];    // tanh of the token's low-rank row
-    __shared__ float scratch[33];
+    extern __shared__ float gp_s[];
+    float* w2_s = gp_s;                              // [D][GP_RC + 1]
+    float* th_s = w2_s + D * (GP_RC + 1);            // [tt_n][GP_RC]: tanh of the tokens' low-rank rows
+    float* len_s = th_s + GP_MAX_TT * GP_RC;         // [tt_n]: the keys' lengths
     fx_pdl_wait();
-    const int t = blockIdx.x, h = blockIdx.y;
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) th_s[r] = tanhf(w1_out[(long)t * ldw1 + r]);
-    const float* kr = k + (long)t * ldk + (long)h * D;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) ss = fmaf(kr[i], kr[i], ss);
-    ss = block_sum(ss, scratch);     // (its barriers also publish th_s)
-    const float len = sqrtf(ss + 1e-6f);
-    const long row = (long)t * H * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        const int c = h * D + i;
-        float z = 0.f;
-        for (int r = 0; r < rank; ++r) z = fmaf(load_any(w2, w2_dtype, (long)c * rank + r), th_s[r], z);
-        z += load_any(w0, w0_dtype, c);
-        const float a = sigmoid_f(a_pre[(long)t * lda + c] + load_any(a_bias, ab_dtype, c));
-        const float uu = kr[i] / len;
-        u[row + c] = uu;
-        au[row + c] = a * uu;
-        w[row + c] = expf(-rate * sigmoid_f(z));
+    const int t0 = blockIdx.x * tt_n, h = blockIdx.y;
+    const int nt = min(tt_n, n_tokens - t0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int tt = warp; tt < nt; tt += GP_THREADS / 32) {
+        const float* kr = k + (long)(t0 + tt) * ldk + (long)h * D;
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) ss = fmaf(kr[i], kr[i], ss);
+        for (int x = 16; x > 0; x >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, x);
+        if (lane == 0) len_s[tt] = sqrtf(ss + 1e-6f);
+    }
+    const int items = nt * D;
+    const bool vec4 = rank % 4 == 0 && (uintptr_t)w2 % 16 == 0;
+    float z[GP_ITEMS];
+#pragma unroll
+    for (int n = 0; n < GP_ITEMS; ++n) z[n] = 0.f;
+    for (int rc0 = 0; rc0 < rank; rc0 += GP_RC) {
+        const int nr = min(GP_RC, rank - rc0);
+        __syncthreads();
+        if (vec4) {     // four columns a load
+            for (int idx = threadIdx.x; idx < D * (GP_RC / 4); idx += GP_THREADS) {
+                const int i = idx / (GP_RC / 4), r = (idx - i * (GP_RC / 4)) * 4;
+                const long at = ((long)h * D + i) * rank + rc0 + r;
+                float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < nr) {    // (nr is a multiple of 4 here)
+                    if (w2_dtype == FX_F32) {
+                        f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w2) + at);
+                    } else {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(w2) + at);
+                        f.x = __uint_as_float(raw.x << 16); f.y = __uint_as_float(raw.x & 0xffff0000u);
+                        f.z = __uint_as_float(raw.y << 16); f.w = __uint_as_float(raw.y & 0xffff0000u);
+                    }
+                }
+                float* dst = w2_s + i * (GP_RC + 1) + r;
+                dst[0] = f.x; dst[1] = f.y; dst[2] = f.z; dst[3] = f.w;
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < D * GP_RC; idx += GP_THREADS) {
+                const int i = idx / GP_RC, r = idx - i * GP_RC;
+                w2_s[i * (GP_RC + 1) + r] = r < nr ? load_any(w2, w2_dtype, ((long)h * D + i) * rank + rc0 + r) : 0.f;
+            }
+        }
+        for (int idx = threadIdx.x; idx < nt * GP_RC; idx += GP_THREADS) {
+            const int tt = idx / GP_RC, r = idx - tt * GP_RC;
+            th_s[idx] = r < nr ? tanhf(w1_out[(long)(t0 + tt) * ldw1 + rc0 + r]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int n = 0; n < GP_ITEMS; ++n) {
+            const int idx = threadIdx.x + n * GP_THREADS;
+            if (idx < items) {
+                const int tt = idx / D, i = idx - tt * D;
+                const float* wr = w2_s + i * (GP_RC + 1);
+                const float* tr = th_s + tt * GP_RC;
+                float acc = z[n];
+                for (int r = 0; r < nr; ++r) acc = fmaf(wr[r], tr[r], acc);
+                z[n] = acc;
+            }
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < GP_ITEMS; ++n) {
+        const int idx = threadIdx.x + n * GP_THREADS;
+        if (idx < items) {
+            const int tt = idx / D, i = idx - tt * D, c = h * D + i;
+            const long t = t0 + tt;
+            const float zz = z[n] + load_any(w0, w0_dtype, c);
+            const float a = sigmoid_f(a_pre[t * lda + c] + load_any(a_bias, ab_dtype, c));
+            const float uu = k[t * ldk + c] / len_s[tt];
+            const long at = t * H * D + c;
+            u[at] = uu;
+            au[at] = a * uu;
+            w[at] = expf(-rate * sigmoid_f(zz));
+        }
     }
 }
 
@@ -94,7 +160,7 @@ template <int RPL>
 __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(const GdArgs a)
 {
     extern __shared__ __align__(16) float sm[];
-    fx_pdl_wait();
+    fx_pdl_wait_only();
     const int b = blockIdx.x, h = blockIdx.y;
     const int R = a.R, cols = GD_THREADS / R, D = a.D, DP = R * RPL;
     const int part = threadIdx.x % R, cl = threadIdx.x / R;
@@ -208,6 +274,7 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(const Gd
         }
         __syncthreads();     // everyone is done with this buffer before the chunk after next is copied into it
     }
+    fx_pdl_trigger();
     if (live) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
@@ -240,11 +307,18 @@ extern "C" int fx_general_delta_prep(const float* k, long ldk, const float* a_pr
                                      int n_tokens, int H, int D, int rank, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
-    if (H <= 0 || H > 65535 || D <= 0 || rank <= 0 || rank > 8192) return FX_ERR_SIZE;
-    int nt = 32;
-    while (nt < D && nt < 256) nt <<= 1;
-    fx_launch_pdl(general_delta_prep_kernel, dim3(n_tokens, H), dim3(nt), (size_t)rank * sizeof(float), (cudaStream_t)stream,
-                  k, ldk, a_pre, lda, w1_out, ldw1, w2, w2_dtype, w0, w0_dtype, a_bias, ab_dtype, rate, u, au, w, H, D, rank);
+    if (H <= 0 || H > 65535 || D <= 0 || D > GD_MAX_D || rank <= 0) return FX_ERR_SIZE;
+    // few tokens (a decode step): a block a token, so that every head's slice of W2 is read by as many blocks as there
+    // are tokens and the step is spread over the device; many: eight tokens share one reading of the slice
+    const int tt_n = n_tokens >= 64 ? GP_MAX_TT : 1;
+    const size_t smem = ((size_t)D * (GP_RC + 1) + GP_MAX_TT * GP_RC + GP_MAX_TT) * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(general_delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    fx_launch_pdl(general_delta_prep_kernel, dim3((unsigned)fx_cdiv(n_tokens, tt_n), H), dim3(GP_THREADS), smem,
+                  (cudaStream_t)stream, k, ldk, a_pre, lda, w1_out, ldw1, w2, w2_dtype, w0, w0_dtype, a_bias, ab_dtype, rate,
+                  u, au, w, n_tokens, H, D, rank, tt_n);
     return fx_launch_status();
 }
 

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     __shared__ float v_s[CH][SCAN_THREADS];
     __shared__ float g_s[CH], b_s[CH];
     __shared__ float rd_s[CH][SCAN_THREADS];
-    fx_pdl_wait();
+    fx_pdl_wait_only();    // the kernel after this one starts when the loop over the tokens is over
     const int b = blockIdx.x, h = blockIdx.y;
     const int R = a.R, cols = SCAN_THREADS / R;
     const int part = threadIdx.x % R, cl = threadIdx.x / R;
@@ -313,6 +313,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 if (tt < nt) a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = rd[tt];
         }
     }
+    fx_pdl_trigger();
     if (live) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {

@@ -307,6 +307,27 @@ def rmsnorm(x, weight, eps, out, rows=None, stream=None):
 GATE_ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2}   # what a gated feed-forward passes its gate through
 
 
+UNARY_ACTIVATIONS = {"relu_square": 1}     # what a plain product's result may pass through in the kernel's epilogue
+
+
+def unary_code(activation) -> int:
+    """The product kernels' code of an activation on their result (0 for None)."""
+    if activation is None:
+        return 0
+    try:
+        return UNARY_ACTIVATIONS[activation]
+    except (KeyError, TypeError):
+        raise KernelError(f"activation {activation!r}: the product kernels know {', '.join(UNARY_ACTIVATIONS)}") from None
+
+
+def _gated_or_unary(gated, unary):
+    """The kernels' ``gated`` argument: the gate's code, or minus the code of a plain product's activation."""
+    u = unary_code(unary)
+    if u and gated:
+        raise KernelError("a gated product takes no second activation")
+    return -u if u else gated
+
+
 def gate_code(activation) -> int:
     """``activation``: a name, or (name, limit, alpha) for the clamped unit
     min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
@@ -883,7 +904,7 @@ def skinny_ok(x, w) -> bool:
             and w.stride(-2) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=None, group_offsets=None,
+def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, unary=None, x_rows=None, group_offsets=None,
                 active_groups=None, tokens_hint=0, transposed_out=False, stream=None):
     """out[rows, N] (+)= x . w^T for few rows: streams ``w`` once.  ``gated``: ``w`` is
     [gate rows ; up rows] (2N rows) and out = silu(gate) * up.  Grouped: ``w`` is
@@ -901,7 +922,7 @@ def gemm_skinny(x, w, out, *, bias=None, accumulate=False, gated=False, x_rows=N
         raise KernelError(f"gemm_skinny shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_skinny", _ptr(x), _rows(x), _ptr(x_rows), _ptr(w), ldw, wstride, _ptr(bias),
          code(bias) if bias is not None else 0, _ptr(out), code(out), _rows(out), int(accumulate), rows, N, K,
-         int(gated), N if gated else 0, lim, alpha, _ptr(group_offsets), _ptr(active_groups), n_slots, int(tokens_hint),
+         int(_gated_or_unary(gated, unary)), N if gated else 0, lim, alpha, _ptr(group_offsets), _ptr(active_groups), n_slots, int(tokens_hint),
          int(transposed_out), stream if stream is not None else stream_ptr())
     return out
 
@@ -1039,7 +1060,7 @@ def tc_ok(x, w) -> bool:
             and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(-1) == 1)
 
 
-def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offsets=None, status=None, stream=None):
+def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, unary=None, group_offsets=None, status=None, stream=None):
     """out[M, N] (+)= x . w^T on the tcgen05 tensor cores.  ``gated``: ``w`` is [gate rows ; up rows] and
     out = silu(gate) * up.  Grouped: ``w`` is [G, rows, K] and the rows of ``x``/``out`` are sorted by group."""
     M, N = out.shape
@@ -1052,12 +1073,12 @@ def gemm_tc(x, w, out, *, bias=None, accumulate=False, gated=False, group_offset
     if wrows != (2 * N if gated else N) or w.shape[-1] != K or x.shape[0] != M:
         raise KernelError(f"gemm_tc shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
-         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, lim, alpha,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(_gated_or_unary(gated, unary)), N if gated else 0, lim, alpha,
          _ptr(group_offsets), G, _ptr(status), stream if stream is not None else stream_ptr())
     return out
 
 
-def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_offsets=None, tokens_per_tile=0,
+def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, unary=None, group_offsets=None, tokens_per_tile=0,
                  weights_first=None, k_splits=1, status=None, stream=None):
     """The same product as :func:`gemm_tc` with the roles swapped: 128 features of ``w`` fill the lanes of a tile,
     the tokens its columns (multiples of 16 up to ``tokens_per_tile``: 32, 64 or 128; 0 = chosen from the sizes).
@@ -1076,7 +1097,7 @@ def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_o
     if wrows != (2 * N if gated else N) or w.shape[-1] != K or x.shape[0] != M:
         raise KernelError(f"gemm_tc_swap shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc_swap", _ptr(x), _rows(x), _ptr(w), ldw, wstride, wrows, _ptr(bias), code(bias) if bias is not None else 0,
-         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, lim, alpha,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(_gated_or_unary(gated, unary)), N if gated else 0, lim, alpha,
          _ptr(group_offsets), G, int(tokens_per_tile),
          int(group_offsets is None if weights_first is None else weights_first), int(k_splits),
          _ptr(torch.empty(k_splits, M, N, dtype=torch.float32, device=out.device)) if k_splits > 1 else None,
@@ -1084,7 +1105,7 @@ def gemm_tc_swap(x, w, out, *, bias=None, accumulate=False, gated=False, group_o
     return out
 
 
-def gemm_tc2(x, w, out, *, bias=None, accumulate=False, gated=False, status=None, stream=None):
+def gemm_tc2(x, w, out, *, bias=None, accumulate=False, gated=False, unary=None, status=None, stream=None):
     """The dense product of :func:`gemm_tc` on pairs of SMs (tcgen05 cta_group::2: 256 x 256 tiles shared by the two
     CTAs of a cluster, each fetching half of the tile's operands).  For prompt-sized dense products."""
     M, N = out.shape
@@ -1093,7 +1114,7 @@ def gemm_tc2(x, w, out, *, bias=None, accumulate=False, gated=False, status=None
     if w.dim() != 2 or w.shape[0] != (2 * N if gated else N) or w.shape[1] != K or x.shape[0] != M:
         raise KernelError(f"gemm_tc2 shapes do not agree: x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
     call("fx_gemm_tc2", _ptr(x), _rows(x), _ptr(w), w.stride(0), w.shape[0], _ptr(bias), code(bias) if bias is not None else 0,
-         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(gated), N if gated else 0, lim, alpha,
+         _ptr(out), code(out), _rows(out), int(accumulate), M, N, K, int(_gated_or_unary(gated, unary)), N if gated else 0, lim, alpha,
          _ptr(status), stream if stream is not None else stream_ptr())
     return out
 
@@ -1139,31 +1160,50 @@ def swap_k_splits(T: int, N: int, K: int) -> int:
     return 0
 
 
-def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None, after_short_kernel=False):
-    """out (+)= x . w^T (+ bias): picks the kernel by size and element type.  ``after_short_kernel``: the kernel before
-    this one on the stream is short and leaves the memory system idle; a few tokens then go to the kernel that asks
-    for the whole matrix before it waits for that kernel (:func:`gemm_slab`), where the matrix fits."""
+def _apply_unary_(out, activation, stream=None):
+    """The activation of :func:`linear` as a step of its own, for the kernels that do not have it in their epilogue."""
+    unary_code(activation)
+    return relu_square_(out, stream=stream)
+
+
+def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None, after_short_kernel=False, activation=None):
+    """out (+)= act(x . w^T (+ bias)): picks the kernel by size and element type.  ``after_short_kernel``: the kernel
+    before this one on the stream is short and leaves the memory system idle; a few tokens then go to the kernel that
+    asks for the whole matrix before it waits for that kernel (:func:`gemm_slab`), where the matrix fits.
+    ``activation`` (None or "relu_square", not with ``accumulate``): in the product's epilogue where the chosen kernel
+    has one for it, as a step of its own on ``out`` otherwise."""
     T = x.shape[0]
+    act = activation
+    if act is not None:
+        unary_code(act)
+        if accumulate:
+            raise KernelError("linear: an activation on a sum that is added to what is there is not defined here")
     if after_short_kernel and T <= SLAB_BETTER_MAX_TOKENS and slab_ok(x, w) and out.dtype in _CODES:
-        return gemm_slab(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
+        gemm_slab(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
+        return _apply_unary_(out, act, stream) if act else out
     if (T > SKINNY_MAX_TOKENS and w.shape[0] <= SKINNY_MAX_TOKENS and bias is None and skinny_ok(w, x)):
         # many tokens, a narrow output (router logits): the weight-streaming kernel with the roles swapped,
         # x streamed once as the "matrix", w as the few "tokens", stored transposed
-        return gemm_skinny(w, x, out, accumulate=accumulate, transposed_out=True, stream=stream)
+        gemm_skinny(w, x, out, accumulate=accumulate, transposed_out=True, stream=stream)
+        return _apply_unary_(out, act, stream) if act else out
     if T <= SKINNY_MAX_TOKENS and w.dim() == 2 and tc_ok(x, w):
         N, K = w.shape
         if T >= 8 and N * K >= (1 << 27):   # the vocabulary head: tiles enough without cutting K
-            return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
+            return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, unary=act, status=status, stream=stream)
         ks = swap_k_splits(T, N, K)
+        if ks > 1:      # the runs' partial sums are added by a second kernel: the activation follows that
+            gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, k_splits=ks, status=status, stream=stream)
+            return _apply_unary_(out, act, stream) if act else out
         if ks:
-            return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, k_splits=ks, status=status, stream=stream)
+            return gemm_tc_swap(x, w, out, bias=bias, accumulate=accumulate, unary=act, status=status, stream=stream)
     if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w):
-        return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
+        return gemm_skinny(x, w, out, bias=bias, accumulate=accumulate, unary=act, stream=stream)
     if T > SKINNY_MAX_TOKENS and tc_ok(x, w):
         if w.dim() == 2 and pairs_better(T, w.shape[0]):
-            return gemm_tc2(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
-        return gemm_tc(x, w, out, bias=bias, accumulate=accumulate, status=status, stream=stream)
-    return gemm(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
+            return gemm_tc2(x, w, out, bias=bias, accumulate=accumulate, unary=act, status=status, stream=stream)
+        return gemm_tc(x, w, out, bias=bias, accumulate=accumulate, unary=act, status=status, stream=stream)
+    gemm(x, w, out, bias=bias, accumulate=accumulate, stream=stream)
+    return _apply_unary_(out, act, stream) if act else out
 
 
 def gated_linear(x, w_gu, out, *, status=None, stream=None, activation="silu"):

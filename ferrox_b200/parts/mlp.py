@@ -52,8 +52,8 @@ class SwigluMlp(FeedForward):
 
 
 class PlainMlp(FeedForward):
-    """down(act(up x)) without a gate; act = the square of ReLU.  The activation runs on the rows the first product
-    wrote, in place."""
+    """down(act(up x)) without a gate; act = the square of ReLU, in the first product's epilogue where its kernel has
+    one (in place on the rows it wrote otherwise)."""
 
     graph_safe = True
     ACTIVATIONS = ("relu_square",)
@@ -79,8 +79,7 @@ class PlainMlp(FeedForward):
 
     def forward_into(self, x, out, batch, accumulate=False):
         act = self.rt.empty(x.shape[0], self.spec.intermediate)
-        ops.linear(x, self.w_up, act, status=batch.status, stream=batch.stream)
-        ops.relu_square_(act, stream=batch.stream)
+        ops.linear(x, self.w_up, act, status=batch.status, stream=batch.stream, activation=self.spec.activation)
         ops.linear(act, self.w_down, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
 
 

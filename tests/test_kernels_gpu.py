@@ -587,6 +587,44 @@ def test_gemm_tc2_pairs_of_sms(M, N, K):
     assert rel(wide[:, :N], want) < 2e-5 and float(wide[:, N:].min()) == 7.0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 60, 64), (8, 200, 96), (33, 4100, 136), (64, 2048, 512), (70, 100, 96),
+                                   (300, 520, 136), (2048, 2048, 264)])
+def test_products_with_the_squared_relu_in_their_epilogue(M, N, K):
+    """Every product kernel that takes an activation on its result, the kernel ``linear`` picks, and ``linear`` where
+    the picked kernel has no epilogue for it (runs of K): relu(x w^T + b)^2, which the plain product and the plain
+    ReLU both miss by far."""
+    o = ops()
+    x, w, bias = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.2), rnd(N, seed=9)
+    z = x.float() @ w.float().T + bias
+    want = torch.relu(z) ** 2
+    assert rel(torch.relu(z), want) > 0.05 and rel(z, want) > 0.05
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels = []
+    if M <= o.SKINNY_MAX_TOKENS:
+        kernels += [lambda *a, **k: o.gemm_tc_swap(*a, status=status, **k)]
+        if o.skinny_ok(x, w):
+            kernels.append(o.gemm_skinny)
+    else:
+        kernels += [lambda *a, **k: o.gemm_tc(*a, status=status, **k), lambda *a, **k: o.gemm_tc2(*a, status=status, **k)]
+    for kern in kernels:
+        for dt, tol in ((torch.float32, 3e-5), (torch.bfloat16, TOL["bfloat16"])):
+            out = torch.full((M, N), 7.0, dtype=dt, device=DEV)
+            kern(x, w, out, bias=bias, unary="relu_square")
+            assert int(status) == 0 and rel(out, want) < tol
+    for after_short in (False, True):
+        out = torch.full((M, N), 7.0, device=DEV)
+        o.linear(x, w, out, bias=bias, status=status, activation="relu_square", after_short_kernel=after_short)
+        assert int(status) == 0 and rel(out, want) < 3e-5
+    x32, w32 = x.float(), w.float()      # 32-bit operands: the generic kernel, then the activation as a step of its own
+    out = torch.full((M, N), 7.0, device=DEV)
+    o.linear(x32, w32, out, bias=bias, activation="relu_square")
+    assert rel(out, want) < 3e-5
+    with pytest.raises(o.KernelError):
+        o.linear(x, w, out, activation="relu_cube")
+    with pytest.raises(o.KernelError):
+        o.gemm_tc_swap(x[:1], torch.cat([w, w]), out[:1], gated=True, unary="relu_square")
+
+
 @pytest.mark.parametrize("M,I,K", [(256, 128, 64), (200, 1408, 256), (70, 100, 96), (2048, 5632, 2048)])
 def test_gemm_tc2_gated(M, I, K):
     o = ops()
