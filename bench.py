@@ -219,13 +219,13 @@ def sesuzen_shape(width, layers, ff, vocab=32768, window=1024, moe=False):
     """Layer sizes that resemble a real model's: generalized-delta layers with heads of 64 (a state of 64 x 64 a head,
     a decay of inner width 64) and attention layers with heads of 128 on a quarter as many key heads, a window of
     1,024 that keeps the first 4 positions, in turn; four taps of input convolution.  The mixers hold 4.75 x width^2
-    parameters a layer on average against 5.625 x width^2 in the Safepel shape; the difference goes into the dense
-    feed-forward.  ``moe``: 60 experts of which a token uses 4 instead, as wide as the Qwen2-MoE shape's."""
+    parameters a layer on average against 5.625 x width^2 in the Safepel shape; the difference goes into the
+    feed-forward, whose two matrices are as large together as the three of the Safepel shape's gated one.  ``moe``: 60 experts of which a token uses 4 instead, as wide as the Qwen2-MoE shape's."""
     h = width // 128
     if moe:
         mlp = {"kind": "moe", "expert": {"ff": width * 11 // 16 // 64 * 64}, "router": {"experts": 60, "top": 4}}
     else:
-        mlp = {"kind": "dense", "ff": (ff + 7 * width // 16 + 63) // 64 * 64}
+        mlp = {"kind": "dense", "ff": (3 * ff // 2 + 7 * width // 16 + 63) // 64 * 64}
     delta = {"type": "general_delta", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "mlp": mlp}
     att = {"type": "attention", "mlp": mlp, "mixer": {
         "heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,

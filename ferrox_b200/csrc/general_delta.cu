@@ -40,19 +40,21 @@ constexpr int GP_RC = 64;           // low-rank channels a pass
 constexpr int GP_MAX_TT = 8;        // tokens a block
 constexpr int GP_ITEMS = GP_MAX_TT * 256 / GP_THREADS;
 
+constexpr int GP_LD = GP_RC + 4;    // floats between two rows of W2 in shared memory
+
 // One block: `tt_n` tokens of one head.  The head's rows of W2 pass through shared memory GP_RC columns at a time
-// (read along their rows, so the loads coalesce, and kept with an odd stride, so the threads of a warp, one key
-// channel each, meet no bank twice); every (token, channel) sums its products in the order of the low-rank index,
-// whatever the block holds beside it.
+// (read along their rows, so the loads coalesce, and kept GP_RC + 4 floats apart, so that eight threads, one key
+// channel each, read 16 bytes each from all 32 banks); every (token, channel) sums its products in the order of the
+// low-rank index, whatever the block holds beside it.
 __global__ void __launch_bounds__(GP_THREADS) general_delta_prep_kernel(
     const float* __restrict__ k, long ldk, const float* __restrict__ a_pre, long lda, const float* __restrict__ w1_out,
     long ldw1, const void* __restrict__ w2, int w2_dtype, const void* __restrict__ w0, int w0_dtype,
     const void* __restrict__ a_bias, int ab_dtype, float rate, float* __restrict__ u, float* __restrict__ au,
     float* __restrict__ w, int n_tokens, int H, int D, int rank, int tt_n)
 {
-    extern __shared__ float gp_s[];
-    float* w2_s = gp_s;                              // [D][GP_RC + 1]
-    float* th_s = w2_s + D * (GP_RC + 1);            // [tt_n][GP_RC]: tanh of the tokens' low-rank rows
+    extern __shared__ __align__(16) float gp_s[];
+    float* w2_s = gp_s;                              // [D][GP_LD]
+    float* th_s = w2_s + D * GP_LD;                  // [tt_n][GP_RC]: tanh of the tokens' low-rank rows
     float* len_s = th_s + GP_MAX_TT * GP_RC;         // [tt_n]: the keys' lengths
     fx_pdl_wait();
     const int t0 = blockIdx.x * tt_n, h = blockIdx.y;
@@ -87,13 +89,12 @@ __global__ void __launch_bounds__(GP_THREADS) general_delta_prep_kernel(
                         f.z = __uint_as_float(raw.y << 16); f.w = __uint_as_float(raw.y & 0xffff0000u);
                     }
                 }
-                float* dst = w2_s + i * (GP_RC + 1) + r;
-                dst[0] = f.x; dst[1] = f.y; dst[2] = f.z; dst[3] = f.w;
+                *reinterpret_cast<float4*>(w2_s + i * GP_LD + r) = f;
             }
         } else {
             for (int idx = threadIdx.x; idx < D * GP_RC; idx += GP_THREADS) {
                 const int i = idx / GP_RC, r = idx - i * GP_RC;
-                w2_s[i * (GP_RC + 1) + r] = r < nr ? load_any(w2, w2_dtype, ((long)h * D + i) * rank + rc0 + r) : 0.f;
+                w2_s[i * GP_LD + r] = r < nr ? load_any(w2, w2_dtype, ((long)h * D + i) * rank + rc0 + r) : 0.f;
             }
         }
         for (int idx = threadIdx.x; idx < nt * GP_RC; idx += GP_THREADS) {
@@ -106,10 +107,14 @@ __global__ void __launch_bounds__(GP_THREADS) general_delta_prep_kernel(
             const int idx = threadIdx.x + n * GP_THREADS;
             if (idx < items) {
                 const int tt = idx / D, i = idx - tt * D;
-                const float* wr = w2_s + i * (GP_RC + 1);
-                const float* tr = th_s + tt * GP_RC;
+                const float4* wr = reinterpret_cast<const float4*>(w2_s + i * GP_LD);
+                const float4* tr = reinterpret_cast<const float4*>(th_s + tt * GP_RC);
                 float acc = z[n];
-                for (int r = 0; r < nr; ++r) acc = fmaf(wr[r], tr[r], acc);
+                for (int r4 = 0; r4 < (nr + 3) >> 2; ++r4) {     // (zeros beyond nr in both rows)
+                    const float4 ww = wr[r4], th = tr[r4];
+                    acc = fmaf(ww.x, th.x, acc); acc = fmaf(ww.y, th.y, acc);
+                    acc = fmaf(ww.z, th.z, acc); acc = fmaf(ww.w, th.w, acc);
+                }
                 z[n] = acc;
             }
         }
@@ -183,28 +188,35 @@ __global__ void __launch_bounds__(GD_THREADS) general_delta_scan_kernel(const Gd
     for (int idx = threadIdx.x; idx < 2 * buf_floats; idx += GD_THREADS) sm[idx] = 0.f;
     __syncthreads();
 
+    // Staging.  Thread t copies piece t, t + 128, ... of a chunk; a piece's (token, place in the row) moves on by the
+    // same step every time, so the quotient and the remainder are taken once here and carried from piece to piece.
+    const int pw = a.vec ? D >> 2 : D;                   // pieces a row: 16 bytes each, or one element
+    const int p_tt0 = threadIdx.x / pw, p_i0 = threadIdx.x - p_tt0 * pw;
+    const int p_dq = GD_THREADS / pw, p_dr = GD_THREADS - p_dq * pw;
+    const int nc = min(cols, D - col0);                  // the block's live columns
+    const int v_tt0 = threadIdx.x / nc, v_c0 = threadIdx.x - v_tt0 * nc;
+    const int v_dq = GD_THREADS / nc, v_dr = GD_THREADS - v_dq * nc;
+    const float* srcp[5];
+#pragma unroll
+    for (int arr = 0; arr < 5; ++arr) srcp[arr] = a.src[arr] + (long)h * D;
+    const float* vp = a.v + (long)h * D + col0;
     auto issue = [&](int c0, int nt, int buf) {
         const uint32_t base = sm_u + (uint32_t)(buf * buf_floats) * 4u;
-        if (a.vec) {
-            const int q4 = D >> 2;
-            for (int idx = threadIdx.x; idx < 5 * nt * q4; idx += GD_THREADS) {
-                const int arr = idx / (nt * q4), rem = idx - arr * nt * q4;
-                const int tt = rem / q4, i4 = rem - tt * q4;
-                cp_async16(base + (uint32_t)((arr * GD_CH + tt) * DP + i4 * 4) * 4u,
-                           a.src[arr] + (long)(c0 + tt) * a.ld[arr] + (long)h * D + i4 * 4);
+        for (int tt = p_tt0, i = p_i0; tt < nt;) {
+            const int e = a.vec ? i * 4 : i;
+#pragma unroll
+            for (int arr = 0; arr < 5; ++arr) {
+                const uint32_t dst = base + (uint32_t)((arr * GD_CH + tt) * DP + e) * 4u;
+                const float* src = srcp[arr] + (long)(c0 + tt) * a.ld[arr] + e;
+                if (a.vec) cp_async16(dst, src); else cp_async4(dst, src);
             }
-        } else {
-            for (int idx = threadIdx.x; idx < 5 * nt * D; idx += GD_THREADS) {
-                const int arr = idx / (nt * D), rem = idx - arr * nt * D;
-                const int tt = rem / D, i = rem - tt * D;
-                cp_async4(base + (uint32_t)((arr * GD_CH + tt) * DP + i) * 4u,
-                          a.src[arr] + (long)(c0 + tt) * a.ld[arr] + (long)h * D + i);
-            }
+            tt += p_dq; i += p_dr;
+            if (i >= pw) { i -= pw; ++tt; }
         }
-        const int nc = min(cols, D - col0);
-        for (int idx = threadIdx.x; idx < nt * nc; idx += GD_THREADS) {
-            const int tt = idx / nc, c = idx - tt * nc;
-            cp_async4(base + (uint32_t)(5 * GD_CH * DP + tt * cols + c) * 4u, a.v + (long)(c0 + tt) * a.ldv + (long)h * D + col0 + c);
+        for (int tt = v_tt0, c = v_c0; tt < nt;) {
+            cp_async4(base + (uint32_t)(5 * GD_CH * DP + tt * cols + c) * 4u, vp + (long)(c0 + tt) * a.ldv + c);
+            tt += v_dq; c += v_dr;
+            if (c >= nc) { c -= nc; ++tt; }
         }
     };
 
@@ -311,7 +323,7 @@ extern "C" int fx_general_delta_prep(const float* k, long ldk, const float* a_pr
     // few tokens (a decode step): a block a token, so that every head's slice of W2 is read by as many blocks as there
     // are tokens and the step is spread over the device; many: eight tokens share one reading of the slice
     const int tt_n = n_tokens >= 64 ? GP_MAX_TT : 1;
-    const size_t smem = ((size_t)D * (GP_RC + 1) + GP_MAX_TT * GP_RC + GP_MAX_TT) * sizeof(float);
+    const size_t smem = ((size_t)D * GP_LD + GP_MAX_TT * GP_RC + GP_MAX_TT) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(general_delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
