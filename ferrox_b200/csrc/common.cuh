@@ -108,10 +108,9 @@ __device__ __forceinline__ void fx_pdl_wait() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// The two halves apart, for a kernel that runs long on few warps (a recurrence over a prompt's tokens): blocks of the
-// kernel after it that were set up early wait on the same SMs and take issue slots from it (a prompt of 2,048 tokens
-// through a delta-rule recurrence on a B200: 1.39 ms beside waiting blocks, 0.65 ms alone).  Such a kernel waits first
-// thing and lets its dependents start when its long loop is over.
+// The two halves apart, for a kernel that runs long on few warps (a recurrence over a prompt's tokens): it waits first
+// thing and lets its dependents be set up when its long loop is over, so that their waiting blocks do not sit on its
+// SMs meanwhile.
 __device__ __forceinline__ void fx_pdl_wait_only() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void fx_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -132,6 +131,23 @@ static inline void fx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block
     cfg.attrs = attr;
     cfg.numAttrs = g_fx_pdl_enabled ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // errors surface through cudaGetLastError
+}
+
+// The same launch with the early set-up left out when `early` is false.  For a kernel that runs long on few blocks (a
+// recurrence over a prompt): blocks that are set up while the kernel before them still fills the device land where its
+// blocks happen to end first, several on one SM beside SMs that get none, and stay there (a recurrence of 128 blocks
+// over 2,048 tokens on a B200: 1.4 ms set up early, 0.65 ms on an empty device).  Its griddepcontrol instructions
+// then do nothing, and the kernel after it may still be set up early.
+template <typename... KArgs, typename... Args>
+static inline void fx_launch_pdl_if(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+    if (early) { fx_launch_pdl(kernel, grid, block, smem, stream, args...); return; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 static inline int fx_launch_status() {

@@ -307,7 +307,8 @@ int launch_gd(const GdArgs& a, int n_entries, cudaStream_t s)
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_entries, a.H, (unsigned)fx_cdiv(a.D, cols));
-    fx_launch_pdl(kern, grid, dim3(GD_THREADS), smem, s, a);
+    // a prompt's recurrence starts on an empty device (see fx_launch_pdl_if); a decode step's is set up early
+    fx_launch_pdl_if(a.n_tokens < 8 * n_entries, kern, grid, dim3(GD_THREADS), smem, s, a);
     return fx_launch_status();
 }
 

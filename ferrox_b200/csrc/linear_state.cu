@@ -330,8 +330,10 @@ void launch_scan(const ScanArgs& a, int n_entries, cudaStream_t s)
 {
     const int cols = SCAN_THREADS / a.R;
     dim3 grid(n_entries, a.H, (unsigned)fx_cdiv(a.V, cols));
-    if (a.beta) fx_launch_pdl(state_scan_kernel<RPL, true, T>, grid, SCAN_THREADS, 0, s, a);
-    else fx_launch_pdl(state_scan_kernel<RPL, false, T>, grid, SCAN_THREADS, 0, s, a);
+    // a prompt's recurrence starts on an empty device (see fx_launch_pdl_if); a decode step's is set up early
+    const bool early = a.n_tokens < 8 * (int)grid.x;
+    if (a.beta) fx_launch_pdl_if(early, state_scan_kernel<RPL, true, T>, grid, SCAN_THREADS, 0, s, a);
+    else fx_launch_pdl_if(early, state_scan_kernel<RPL, false, T>, grid, SCAN_THREADS, 0, s, a);
 }
 
 template <typename T>
