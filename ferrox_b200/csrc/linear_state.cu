@@ -377,6 +377,28 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(
     }
 }
 
+// The same for narrow groups (up to 64 elements): a warp a group, four groups a block, no barrier.
+template <typename GT, typename OT>
+__global__ void __launch_bounds__(128) gated_group_norm_warp_kernel(
+    const float* __restrict__ x, const GT* __restrict__ gate, long ldg, const void* __restrict__ w, int w_dtype,
+    float eps, int act, OT* __restrict__ out, int groups, int width, long w_stride)
+{
+    fx_pdl_wait();
+    const int t = blockIdx.x, grp = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (grp >= groups) return;
+    const float* xr = x + ((long)t * groups + grp) * width;
+    const GT* gr = gate + (long)t * ldg + (long)grp * width;
+    float ss = 0.f;
+    for (int i = lane; i < width; i += 32) ss = fmaf(xr[i], xr[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    OT* o = out + ((long)t * groups + grp) * width;
+    for (int i = lane; i < width; i += 32) {
+        const float gv = to_f32(gr[i]);
+        o[i] = from_f32<OT>(xr[i] * inv * load_any(w, w_dtype, (long)grp * w_stride + i) * (act ? sigmoid_f(gv) : silu_f(gv)));
+    }
+}
+
 }  // namespace
 
 extern "C" int fx_delta_prep(const void* proj, int dtype, long ldp, const void* conv_w, int cw_dtype, int taps,
@@ -462,13 +484,19 @@ extern "C" int fx_gated_group_norm(const float* x, const void* gate, int gate_dt
     if (n_tokens <= 0) return FX_OK;
     if (groups <= 0 || width <= 0) return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(n_tokens, groups);
-    if (gate_dtype == FX_F32 && out_dtype == FX_F32)
-        fx_launch_pdl(gated_group_norm_kernel<float, float>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (float*)out, groups, width, w_stride);
-    else if (gate_dtype == FX_F32 && out_dtype == FX_BF16)
-        fx_launch_pdl(gated_group_norm_kernel<float, bf16>, grid, 128, 0, s, x, (const float*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width, w_stride);
-    else if (gate_dtype == FX_BF16 && out_dtype == FX_BF16)
-        fx_launch_pdl(gated_group_norm_kernel<bf16, bf16>, grid, 128, 0, s, x, (const bf16*)gate, ldg, w, w_dtype, eps, act, (bf16*)out, groups, width, w_stride);
+    const bool narrow = width <= 64;
+    dim3 grid(n_tokens, narrow ? (unsigned)fx_cdiv(groups, 4) : groups);
+#define FX_GO(GT, OT)                                                                                                     \
+    do {                                                                                                                  \
+        if (narrow) fx_launch_pdl(gated_group_norm_warp_kernel<GT, OT>, grid, 128, 0, s, x, (const GT*)gate, ldg, w, w_dtype, \
+                                  eps, act, (OT*)out, groups, width, w_stride);                                         \
+        else fx_launch_pdl(gated_group_norm_kernel<GT, OT>, grid, 128, 0, s, x, (const GT*)gate, ldg, w, w_dtype, eps, act, \
+                           (OT*)out, groups, width, w_stride);                                                          \
+    } while (0)
+    if (gate_dtype == FX_F32 && out_dtype == FX_F32) FX_GO(float, float);
+    else if (gate_dtype == FX_F32 && out_dtype == FX_BF16) FX_GO(float, bf16);
+    else if (gate_dtype == FX_BF16 && out_dtype == FX_BF16) FX_GO(bf16, bf16);
     else return FX_ERR_DTYPE;
+#undef FX_GO
     return fx_launch_status();
 }
