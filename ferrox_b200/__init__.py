@@ -11,6 +11,7 @@ from .models import qwen2_moe as _qwen2_moe  # noqa: F401  (registers the archit
 from .models import safepel as _safepel  # noqa: F401  (registers the architecture)
 from .models import bobepel as _bobepel  # noqa: F401  (registers the architecture)
 from .models import sesuzen as _sesuzen  # noqa: F401  (registers the architecture)
+from .models import zanezen as _zanezen  # noqa: F401  (registers the architecture)
 from .parts.base import register_part  # noqa: F401
 from .weights.loader import WeightsError  # noqa: F401
 from .weights.random_init import write_random_model  # noqa: F401

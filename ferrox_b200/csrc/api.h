@@ -18,7 +18,10 @@ int fx_sm_count();
 int fx_set_pdl(int on);
 
 int fx_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens, int hidden, int vocab,
-             int* status, void* stream);
+             int* status, float scale, void* stream);    // out[t] = table[ids[t]] * scale
+// h[r] += scale * y[r] and, with a weight w, x_out[r] = rmsnorm(h[r]) * w on the new rows (elementwise.cu)
+int fx_scaled_add_norm(float* h, const float* y, float scale, const void* w, int w_dtype, float eps, void* x_out,
+                       int x_dtype, int n_rows, int hidden, void* stream);
 int fx_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, float eps, void* out, int out_dtype,
                int n_rows, int hidden, void* stream);
 int fx_silu_mul(const void* gu, long ld_in, void* out, long ld_out, int dtype, const int* n_rows_dev, int rows, int n,
@@ -46,7 +49,9 @@ int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const void* k_page
                           int dtype, const int* block_table, int table_width, int page_size, const int* positions,
                           const int* token_seq, const int* seq_slot, void* out, long ldo, long ldoh, int n_tokens,
                           int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale, float softcap,
-                          const float* slopes, int keep_first, void* stream);
+                          const float* slopes, int keep_first, const float* sinks, int value_share, void* stream);
+// sinks (optional, one per head): exp(sinks[h]) joins the softmax's denominator once.  value_share >= 1: that many
+// consecutive key heads read one value head (the value pages hold n_kv_heads / value_share heads).
 
 // the same operation in bfloat16 on the tensor cores (attention_general_mma.cu); items: int32 [n_items, 5] = (first flat
 // token, tokens, entry, first query head, heads) or nullptr (one token a tile, n_items = tokens)
@@ -55,7 +60,8 @@ int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages
                          const long* kv_strides, const int* block_table, int table_width, int page_size, const int* positions,
                          const int* token_seq, const int* seq_slot, const int* items, int n_items, void* out, long ldo,
                          long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window, float scale,
-                         const float* slopes, int n_splits, float* part_o, float* part_ml, int keep_first, void* stream);
+                         const float* slopes, int n_splits, float* part_o, float* part_ml, int keep_first, float softcap,
+                         const float* sinks, int value_share, void* stream);
 
 int fx_prefill_attention_tc(const void* q, long ldq, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                             const int* block_table, int table_width, int page_size, const int* items, int n_items,
@@ -67,8 +73,11 @@ int fx_prefill_attention(const void* q, long ldq, const void* k_pages, const voi
                          long ldo, int n_heads, int n_kv_heads, int head_dim, int window, float scale, float softcap,
                          void* stream);
 
+// Routing extras (the last three arguments before the stream of the four routing entry points): choice_bias, one
+// number per expert added to sigmoid(logit) for the choice only (mode bit 1; nullptr: none); weight_scale, a factor on
+// the final weights; renorm_eps, added to the sum the kept scores are divided by (mode bit 0).
 int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
-                   float* weights, void* stream);
+                   float* weights, const float* choice_bias, float weight_scale, float renorm_eps, void* stream);
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
                  int* inv_perm, int* active, int n_slots, void* stream);
 
@@ -92,13 +101,17 @@ int fx_gather_rows(const void* x, long ldx, const int* rows, void* out, long ldo
 int fx_gather_rows_scaled(const void* x, long ldx, const int* rows, const int* inv_perm, const float* weights, int top_k,
                           void* out, long ldo, int dtype, int n_rows, int width, void* stream);
 int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
-             int* scratch, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
+             int* scratch, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots,
+             const float* choice_bias, float weight_scale, float renorm_eps, void* stream);
 int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids, float* weights,
-                   int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, void* stream);
+                   int* offsets, int* src_token, int* inv_perm, int* active, int n_slots, const float* choice_bias,
+                   float weight_scale, float renorm_eps, void* stream);
 int fx_route_fused(const void* X, long ldx, const void* W, long ldw, int n_tokens, int n_route, int n_experts, int hidden,
                    int top_k, int renorm, float* logits, long ldl, int* ids, float* weights, int* offsets, int* src_token,
-                   int* inv_perm, int* active, int n_slots, void* xp_out, long ldxp, void* stream);
-int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, void* stream);
+                   int* inv_perm, int* active, int n_slots, void* xp_out, long ldxp, const float* choice_bias,
+                   float weight_scale, float renorm_eps, void* stream);
+int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin, float magnitude,
+                  void* stream);   // cos and sin times `magnitude`
 // A few tokens against a plain matrix that fits the shared memory of all SMs together (gemm_slab.cu): every block asks
 // for its whole slab of W before it waits for the kernel before it on the stream, which therefore must not have written W.
 // C[t, n] (+)= sum_k X[t, k] W[n, k] (+ bias[n]); bfloat16 X and W, K a multiple of 128, C bfloat16 or float32.
@@ -150,11 +163,12 @@ int fx_latent_prep(void* q, long ldq, const void* dkv, long ld_dkv, int dtype, c
                    const int* token_seq, const int* seq_slot, const void* wc, int w_dtype, float eps, const float* cos_sin,
                    int rot_dims, void* q_plain, void* q_full, void* pages, const int* block_table, int table_width,
                    int page_size, int n_tokens, int n_heads, int plain_dim, int rot_dim, int rank, int write_cache,
-                   int* status, void* stream);   // q_plain == nullptr: q's rotated parts are turned where they lie
+                   int* status, int pairing, void* stream);   // q_plain == nullptr: q's rotated parts are turned where they
+                                                              // lie; pairing 1: neighbours, 0: halves
 int fx_rmsnorm_rows(const void* x, int x_dtype, long ldx, const void* w, int w_dtype, float eps, void* out, int out_dtype,
                     long ldo, int n_rows, int n, void* stream);
 int fx_heads_to_tokens(const void* in, long in_ldt, long in_ldh, const void* gate, long ldg, void* out, long ldo, int dtype,
-                       int n_tokens, int n_heads, int width, void* stream);
+                       int n_tokens, int n_heads, int width, int gate_per_head, void* stream);
 
 // softcap c > 0 (fx_paged_attention, fx_prefill_attention, fx_decode_attention): the scaled scores pass through
 // c * tanh(s / c) before the softmax; 0: none.  The kernels that stream pages by TMA take no cap: fx_decode_attention
@@ -217,7 +231,7 @@ int fx_general_delta_scan(const float* r, long ldr, const float* k, long ldk, co
 // update_tail: every entry brings exactly one token and the kernel moves the tail on itself.
 int fx_input_conv(const void* x, int dtype, long ldx, const void* w, int w_dtype, int taps, float* tail,
                   const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int channels,
-                  int update_tail, void* stream);
+                  int update_tail, int add_input, void* stream);   // add_input 0: out[t] = the sum alone
 // out[t] = table[ids[t]] + pos_table[positions[t]] in 32 bits; status 1: an id outside the vocabulary, 4: a position
 // outside the table.
 int fx_embed_pos(const void* table, int dtype, const int* ids, const void* pos_table, int pos_dtype, const int* positions,
@@ -226,6 +240,30 @@ int fx_embed_pos(const void* table, int dtype, const int* ids, const void* pos_t
 int fx_softcap(float* x, long n, float cap, void* stream);
 // x <- max(x, 0)^2 in place, rows of `n` elements with row stride ld.
 int fx_relu_square(void* x, int dtype, long ld, int rows, int n, void* stream);
+
+// The matrix memory of an mLSTM mixer (mlstm.cu): gates capped and taken to the logarithm, a running maximum, the
+// state S [slots, H, V, D], a normaliser n [slots, H, Z, D] and the maximum m [slots, H, Z], Z =
+// fx_mlstm_column_blocks(D, V) copies of both; q, k [tokens, H*D], v [tokens, H*V] and gates [tokens, >= 2H] (input
+// gates, then forget gates, before bias and cap) are 32-bit rows.
+int fx_mlstm_column_blocks(int D, int V);
+int fx_mlstm_scan(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, const float* gates,
+                  long ldg, const void* i_bias, const void* f_bias, int bias_dtype, float cap, float q_scale, float* S,
+                  float* n, float* m, float* out, long ldo, const int* token_seq, const int* seq_slot, int n_tokens,
+                  int n_entries, int H, int D, int V, int copies, void* stream);   // copies: Z as the state holds it
+
+// diff_attention.cu.  fx_conv_rotary_store: a short causal convolution on every channel of the projected
+// [q | k | v] rows (no input added), rotation of the first rot_dims elements of every q and k head by cos_sin
+// [tokens][rot_dims / 2][2], q into q_out, k and v into pages of their own head counts and widths.
+// fx_diff_combine: out[t, h] = rms(a1 - lambda a2) * post, the two maps of head h = g * group + hg being rows
+// (2 g) * group + hg and (2 g + 1) * group + hg of attn.
+int fx_conv_rotary_store(const void* proj, int dtype, long ldp, const void* w, int w_dtype, int taps, float* tail,
+                         const int* positions, const int* token_seq, const int* seq_slot, const float* cos_sin,
+                         int rot_dims, int pairing, void* q_out, long ldq, void* k_pages, void* v_pages,
+                         const int* block_table, int table_width, int page_size, int n_tokens, int n_q_heads,
+                         int n_k_heads, int head_dim, int n_v_heads, int value_dim, int write_cache, int update_tail,
+                         int* status, void* stream);
+int fx_diff_combine(const void* attn, long lda, void* out, long ldo, int dtype, int n_tokens, int n_heads, int group,
+                    int value_dim, float lambda, float eps, float post, void* stream);
 
 #ifdef __cplusplus
 }

@@ -72,6 +72,10 @@ struct GArgs {
     int n_splits;     // > 1 (only without items): blockIdx.z takes one run of the token's keys
     float* part_o;    // [tokens][heads][n_splits][value_dim] unnormalised sums, relative to the run's maximum
     float* part_ml;   // [tokens][heads][n_splits][2] the run's maximum (in units of log2 e) and its sum
+    float softcap;    // c > 0: the scaled scores pass through c tanh(s / c); cap_log2e = c log2 e
+    float cap_log2e, scale_over_cap;
+    const float* sinks;   // (optional, one per head) exp(sinks[h]) joins the softmax's denominator once
+    int value_share;      // consecutive key heads that read one value head
 };
 
 // DVMAX: most value columns one warp accumulates.  NSPLIT: sets of 4 warps that share out the value columns.
@@ -152,7 +156,7 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
             int page = -1;
             if (key <= last_pos && (key >= key_lo || key < keep)) page = table[key / a.page_size];
             const bool ok = page >= 0;
-            const long at = ok ? (long)page * a.v_page_stride + (long)kvh * a.v_head_stride + (long)(key % a.page_size) * a.ldv : 0;
+            const long at = ok ? (long)page * a.v_page_stride + (long)(kvh / a.value_share) * a.v_head_stride + (long)(key % a.page_size) * a.ldv : 0;
             cp_async16(v_u + (buf * BKEY + r) * pv + ch * 16, a.v_pages + at + ch * 8, ok ? 16 : 0);
         }
     };
@@ -211,6 +215,15 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
             }
             // ---- scale, distance bias, mask by absolute position, online softmax (all in units of log2 e) ----
             float mx0 = -INFINITY, mx1 = -INFINITY;
+            if (a.softcap > 0.f) {
+                // the cap: c tanh(scale s / c), then in units of log2 e like the uncapped scores times scale_log2e
+                const float back = a.cap_log2e / a.scale_log2e;
+#pragma unroll
+                for (int j = 0; j < BKEY / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[j][e] = back * tanhf(s[j][e] * a.scale_over_cap);
+                }
+            }
 #pragma unroll
             for (int j = 0; j < BKEY / 8; ++j) {
 #pragma unroll
@@ -286,7 +299,14 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
         return;
     }
     // ---- normalise and store ---------------------------------------------------------
-    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (a.sinks) {
+        // the head's sink in the denominator, once: sums and maximum brought to the larger of the two references
+        const float k0 = a.sinks[head0 + min(r0, rows - 1) % n_h] * 1.4426950408889634f;
+        const float k1 = a.sinks[head0 + min(r1, rows - 1) % n_h] * 1.4426950408889634f;
+        if (l0 > 0.f) { const float mm = fmaxf(m0, k0), f = exp2f(m0 - mm); inv0 = f / (l0 * f + exp2f(k0 - mm)); }
+        if (l1 > 0.f) { const float mm = fmaxf(m1, k1), f = exp2f(m1 - mm); inv1 = f / (l1 * f + exp2f(k1 - mm)); }
+    }
     bf16* o0 = a.out + (long)(tok0 + min(r0, rows - 1) / n_h) * a.ldo + (long)(head0 + min(r0, rows - 1) % n_h) * a.ldoh + col0;
     bf16* o1 = a.out + (long)(tok0 + min(r1, rows - 1) / n_h) * a.ldo + (long)(head0 + min(r1, rows - 1) % n_h) * a.ldoh + col0;
 #pragma unroll
@@ -302,7 +322,7 @@ __global__ void __launch_bounds__(128 * NSPLIT) general_attention_kernel(GArgs a
 // One block a (token, head): the runs of a token's keys added up, each weighted by 2^(its maximum - the largest).
 __global__ void general_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      const int* __restrict__ positions, bf16* __restrict__ out, long ldo, long ldoh,
-                                     int n_heads, int value_dim, int n_splits, int window)
+                                     int n_heads, int value_dim, int n_splits, int window, const float* __restrict__ sinks)
 {
     fx_pdl_wait();
     const int tkn = blockIdx.x, h = blockIdx.y;
@@ -313,8 +333,14 @@ __global__ void general_merge_kernel(const float* __restrict__ part_o, const flo
     float mm = -INFINITY;
     for (int s = 0; s < n_splits; ++s)
         if (has_keys(s)) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    float sunk = 0.f;        // the head's sink: a term of the denominator that no run holds
+    if (sinks && mm != -INFINITY) {
+        const float sk = sinks[h] * 1.4426950408889634f;
+        mm = fmaxf(mm, sk);
+        sunk = exp2f(sk - mm);
+    }
     for (int e = threadIdx.x; e < value_dim; e += blockDim.x) {
-        float ll = 0.f, acc = 0.f;
+        float ll = sunk, acc = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             if (!has_keys(s)) continue;
             const float ms = part_ml[(base + s) * 2];
@@ -339,7 +365,7 @@ int launch(dim3 grid, size_t smem, cudaStream_t s, const GArgs& a)
     if (a.n_splits > 1)
         fx_launch_pdl(general_merge_kernel, dim3(grid.x, a.n_heads), dim3(64), 0, s, (const float*)a.part_o,
                       (const float*)a.part_ml, a.positions, a.out, a.ldo, a.ldoh, a.n_heads, a.value_dim, a.n_splits,
-                      a.window);
+                      a.window, a.sinks);
     return fx_launch_status();
 }
 
@@ -370,6 +396,9 @@ extern "C" int fx_general_attention_ok(int key_dim, int value_dim, int alias)
 
 // items: int32 [n_items, 5] = (first flat token, tokens, entry, first query head, heads), heads of one kv head,
 // tokens x heads <= 64; or nullptr: one token a tile, n_items = tokens.  bfloat16 only.
+// softcap c > 0: the scaled scores pass through c tanh(s / c) before bias and softmax.  sinks (optional, one per
+// head): exp(sinks[h]) joins the denominator once (with runs: in the merge).  value_share >= 1: that many consecutive
+// key heads read one value head (value head = key head / value_share).
 // kv_strides: nullptr for pages laid out [page][kv head][position][ld]; else (k page stride, k head stride, v page
 // stride, v head stride) in elements, for keys and values that lie otherwise (rows of all heads side by side).
 extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const void* k_pages, const void* v_pages, long ldk,
@@ -377,12 +406,14 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
                                     const int* positions, const int* token_seq, const int* seq_slot, const int* items,
                                     int n_items, void* out, long ldo, long ldoh, int n_heads, int n_kv_heads,
                                     int key_dim, int value_dim, int window, float scale, const float* slopes,
-                                    int n_splits, float* part_o, float* part_ml, int keep_first, void* stream)
+                                    int n_splits, float* part_o, float* part_ml, int keep_first, float softcap,
+                                    const float* sinks, int value_share, void* stream)
 {
     if (n_items <= 0) return FX_OK;
-    if (n_kv_heads <= 0 || n_heads % n_kv_heads) return FX_ERR_SIZE;
+    if (value_share < 1) value_share = 1;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_kv_heads % value_share) return FX_ERR_SIZE;
     const long kps = kv_strides ? kv_strides[0] : (long)n_kv_heads * page_size * ldk, khs = kv_strides ? kv_strides[1] : (long)page_size * ldk;
-    const long vps = kv_strides ? kv_strides[2] : (long)n_kv_heads * page_size * ldv, vhs = kv_strides ? kv_strides[3] : (long)page_size * ldv;
+    const long vps = kv_strides ? kv_strides[2] : (long)(n_kv_heads / value_share) * page_size * ldv, vhs = kv_strides ? kv_strides[3] : (long)page_size * ldv;
     const int alias = v_pages == k_pages && ldv == ldk && kps == vps && khs == vhs && value_dim <= key_dim;
     if (!fx_general_attention_ok(key_dim, value_dim, alias)) return FX_ERR_SIZE;
     if (kps % 8 || khs % 8 || vps % 8 || vhs % 8) return FX_ERR_ALIGN;
@@ -399,6 +430,9 @@ extern "C" int fx_general_attention(const void* q, long ldq, long ldqh, const vo
     a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.window = window;
     a.keep_first = (window > 0 && keep_first > 0) ? keep_first : 0;
     a.scale_log2e = scale * 1.4426950408889634f; a.slopes = slopes; a.alias = alias;
+    a.softcap = softcap > 0.f ? softcap : 0.f;
+    a.cap_log2e = a.softcap * 1.4426950408889634f; a.scale_over_cap = a.softcap > 0.f ? scale / a.softcap : 0.f;
+    a.sinks = sinks; a.value_share = value_share;
     a.n_splits = n_splits > 1 ? n_splits : 1; a.part_o = part_o; a.part_ml = part_ml;
     if (a.n_splits > 1 && (items || !part_o || !part_ml || a.n_splits > 65535)) return FX_ERR_SIZE;
     const int bkey = general_bkey(key_dim, value_dim, alias);

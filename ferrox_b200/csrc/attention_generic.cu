@@ -29,6 +29,9 @@
 // slopes[h] * (i - j), a bias that grows with the distance.
 // `keep_first` (with a window): the first keep_first positions of the request stay visible beside the window; they
 // are taken first, in blocks of 32 from position 0, then the window's keys as ever.
+// `sinks` (optional, one per head): exp(sinks[h]) is added to the softmax's denominator, once, unscaled.
+// `value_share` (>= 1): that many consecutive key heads read one value head (value head = key head / value_share;
+// the value pages hold n_kv_heads / value_share heads), for attention maps of their own keys over shared values.
 #include "common.cuh"
 #include "api.h"
 
@@ -44,7 +47,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     long ldk, long ldv, const int* __restrict__ block_table, int table_width, int page_size,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
     T* __restrict__ out, long ldo, long ldoh, int n_heads, int n_kv_heads, int key_dim, int value_dim, int window,
-    float scale, float softcap, const float* __restrict__ slopes, int keep_first)
+    float scale, float softcap, const float* __restrict__ slopes, int keep_first, const float* __restrict__ sinks,
+    int value_share)
 {
     __shared__ float q_s[WARPS][MAX_DK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -52,6 +56,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     const int h = blockIdx.y * WARPS + warp;
     if (h >= n_heads) return;  // whole warp leaves; no block-wide barrier below
     const int kvh = h / (n_heads / n_kv_heads);
+    const int vh = kvh / value_share, n_v_heads = n_kv_heads / value_share;   // key heads that read one value head
     const int pos = positions[t];
     const int* table = block_table + (long)seq_slot[token_seq[t]] * table_width;
     const T* qh = q + (long)t * ldq + (long)h * ldqh;
@@ -76,11 +81,13 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
         const int key = kb + lane;
         bool valid = kept ? key < kept_end : (key >= lo && key <= pos);
         long place = -1;      // (page, kv head, position in the page) as one index
+        long vplace = -1;     // the same for the value head
         float s = -INFINITY;
         const int page = valid ? table[key / page_size] : -1;
         valid = valid && page >= 0;  // a position without a page is skipped, never dereferenced
         if (valid) {
             place = ((long)page * n_kv_heads + kvh) * page_size + (key % page_size);
+            vplace = ((long)page * n_v_heads + vh) * page_size + (key % page_size);
             const T* kr = k_pages + place * ldk;
             float dot = 0.f;
             for (int i = 0; i < key_dim; ++i) dot = fmaf(q_s[warp][i], to_f32(kr[i]), dot);
@@ -97,7 +104,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
         for (int i = 0; i < NV; ++i) acc[i] *= alpha;
         for (int j = 0; j < 32; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
-            const long bj = __shfl_sync(0xffffffffu, place, j);
+            const long bj = __shfl_sync(0xffffffffu, vplace, j);
             if (bj < 0) continue;  // uniform across the warp
             const T* vr = v_pages + bj * ldv;
 #pragma unroll
@@ -107,6 +114,13 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
             }
         }
         m = m_new;
+    }
+    if (sinks && m != -INFINITY) {
+        // a learned number per head in the denominator: it has no key and no value, and counts once
+        const float sk = sinks[h], mm = fmaxf(m, sk), f = expf(m - mm);
+        l = l * f + expf(sk - mm);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) acc[i] *= f;
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     T* o = out + (long)t * ldo + (long)h * ldoh;
@@ -122,13 +136,14 @@ int launch_paged(const void* q, long ldq, long ldqh, const void* k_pages, const 
                  const int* block_table, int table_width, int page_size, const int* positions, const int* token_seq,
                  const int* seq_slot, void* out, long ldo, long ldoh, int n_tokens, int n_heads, int n_kv_heads,
                  int key_dim, int value_dim, int window, float scale, float softcap, const float* slopes, int keep_first,
-                 cudaStream_t s)
+                 const float* sinks, int value_share, cudaStream_t s)
 {
     dim3 grid(n_tokens, (unsigned)fx_cdiv(n_heads, WARPS));
 #define FX_GO(NV)                                                                                                     \
     paged_attention_kernel<T, NV><<<grid, WARPS * 32, 0, s>>>((const T*)q, ldq, ldqh, (const T*)k_pages,              \
         (const T*)v_pages, ldk, ldv, block_table, table_width, page_size, positions, token_seq, seq_slot, (T*)out,    \
-        ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap, slopes, keep_first)
+        ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap, slopes, keep_first, sinks,        \
+        value_share)
     if (value_dim <= 64) FX_GO(2);
     else if (value_dim <= 128) FX_GO(4);
     else if (value_dim <= 256) FX_GO(8);
@@ -146,9 +161,12 @@ extern "C" int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const v
                                      int page_size, const int* positions, const int* token_seq, const int* seq_slot,
                                      void* out, long ldo, long ldoh, int n_tokens, int n_heads, int n_kv_heads,
                                      int key_dim, int value_dim, int window, float scale, float softcap,
-                                     const float* slopes, int keep_first, void* stream)
+                                     const float* slopes, int keep_first, const float* sinks, int value_share,
+                                     void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (value_share < 1) value_share = 1;
+    if (n_kv_heads % value_share) return FX_ERR_SIZE;
     if (keep_first < 0 || window <= 0) keep_first = 0;
     if (key_dim > MAX_DK || value_dim > MAX_DV || key_dim <= 0 || value_dim <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || ldk < key_dim || ldv < value_dim)
@@ -157,11 +175,11 @@ extern "C" int fx_paged_attention_ex(const void* q, long ldq, long ldqh, const v
     if (dtype == FX_F32)
         return launch_paged<float>(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, table_width, page_size,
                                    positions, token_seq, seq_slot, out, ldo, ldoh, n_tokens, n_heads, n_kv_heads,
-                                   key_dim, value_dim, window, scale, softcap, slopes, keep_first, s);
+                                   key_dim, value_dim, window, scale, softcap, slopes, keep_first, sinks, value_share, s);
     if (dtype == FX_BF16)
         return launch_paged<bf16>(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, table_width, page_size,
                                   positions, token_seq, seq_slot, out, ldo, ldoh, n_tokens, n_heads, n_kv_heads,
-                                  key_dim, value_dim, window, scale, softcap, slopes, keep_first, s);
+                                  key_dim, value_dim, window, scale, softcap, slopes, keep_first, sinks, value_share, s);
     return FX_ERR_DTYPE;
 }
 
@@ -174,5 +192,5 @@ extern "C" int fx_paged_attention(const void* q, long ldq, const void* k_pages, 
 {
     return fx_paged_attention_ex(q, ldq, head_dim, k_pages, v_pages, head_dim, head_dim, dtype, block_table, table_width,
                                  page_size, positions, token_seq, seq_slot, out, ldo, head_dim, n_tokens, n_heads,
-                                 n_kv_heads, head_dim, head_dim, window, scale, softcap, nullptr, 0, stream);
+                                 n_kv_heads, head_dim, head_dim, window, scale, softcap, nullptr, 0, nullptr, 1, stream);
 }

@@ -96,8 +96,10 @@ __global__ void latent_prep_kernel(T* __restrict__ q, long ldq, const T* __restr
                                    const float* __restrict__ cos_sin, int rot_dims, T* __restrict__ q_plain,
                                    T* __restrict__ q_full, T* __restrict__ pages, const int* __restrict__ block_table,
                                    int table_width, int page_size, int n_tokens, int H, int D, int R, int C,
-                                   int write_cache, int* __restrict__ status)
+                                   int write_cache, int* __restrict__ status, int pairing)
 {
+    // pairing 1: neighbours (2i, 2i + 1); 0: halves (i, i + rot_dims / 2).  Thread i < half turns pair i; the
+    // threads beyond copy element rot_dims + (i - half).
     __shared__ float scratch[33];
     fx_pdl_wait();
     const int t = blockIdx.x;
@@ -124,9 +126,10 @@ __global__ void latent_prep_kernel(T* __restrict__ q, long ldq, const T* __restr
         T* x = qr + (long)h * (D + R) + D;
         T* o = q_plain ? q_full + ((long)h * n_tokens + t) * W + C : x;   // no head-by-head copy: turned where it lies
         if (i < half) {
-            const float a = to_f32(x[2 * i]), b = to_f32(x[2 * i + 1]), c = cs[2 * i], s = cs[2 * i + 1];
-            o[2 * i] = from_f32<T>(a * c - b * s);
-            o[2 * i + 1] = from_f32<T>(b * c + a * s);
+            const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+            const float a = to_f32(x[ia]), b = to_f32(x[ib]), c = cs[2 * i], s = cs[2 * i + 1];
+            o[ia] = from_f32<T>(a * c - b * s);
+            o[ib] = from_f32<T>(b * c + a * s);
         } else {
             o[half + i] = x[half + i];      // beyond the rotated pairs: element rot_dims + (i - half)
         }
@@ -141,9 +144,10 @@ __global__ void latent_prep_kernel(T* __restrict__ q, long ldq, const T* __restr
     for (int i = threadIdx.x; i < R - half; i += blockDim.x) {
         const T* x = d + C;
         if (i < half) {
-            const float a = to_f32(x[2 * i]), b = to_f32(x[2 * i + 1]), c = cs[2 * i], s = cs[2 * i + 1];
-            dst[C + 2 * i] = from_f32<T>(a * c - b * s);
-            dst[C + 2 * i + 1] = from_f32<T>(b * c + a * s);
+            const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+            const float a = to_f32(x[ia]), b = to_f32(x[ib]), c = cs[2 * i], s = cs[2 * i + 1];
+            dst[C + ia] = from_f32<T>(a * c - b * s);
+            dst[C + ib] = from_f32<T>(b * c + a * s);
         } else {
             dst[C + half + i] = x[half + i];
         }
@@ -168,10 +172,11 @@ __global__ void rmsnorm_rows_kernel(const TI* __restrict__ x, long ldx, const vo
 
 // out[t][h * V + v] = in[t * in_ldt + h * in_ldh + v] * (gate ? sigmoid(gate[t][h * V + v]) : 1): rows laid out head
 // by head ([h][t][v]: in_ldh = tokens * V, in_ldt = V) back into token rows, with the output gate of the mixer applied
+// (gate_per_head: one gate a head, gate[t][h], instead of one an element)
 // on the way; or token rows gated where they lie (in == out, in_ldt = ldo, in_ldh = V).
 template <typename T>
 __global__ void heads_to_tokens_kernel(const T* in, long in_ldt, long in_ldh, const T* __restrict__ gate, long ldg, T* out,
-                                       long ldo, int n_tokens, int H, int V)
+                                       long ldo, int n_tokens, int H, int V, int gate_per_head)
 {
     fx_pdl_wait();
     const long total = (long)n_tokens * H * V;
@@ -180,7 +185,7 @@ __global__ void heads_to_tokens_kernel(const T* in, long in_ldt, long in_ldh, co
         const int c = (int)(idx - (long)t * H * V);
         const int h = c / V, v = c - h * V;
         float x = to_f32(in[(long)t * in_ldt + (long)h * in_ldh + v]);
-        if (gate) x *= 1.0f / (1.0f + expf(-to_f32(gate[(long)t * ldg + c])));
+        if (gate) x *= 1.0f / (1.0f + expf(-to_f32(gate[(long)t * ldg + (gate_per_head ? h : c)])));
         out[(long)t * ldo + c] = from_f32<T>(x);
     }
 }
@@ -218,9 +223,11 @@ extern "C" int fx_latent_prep(void* q, long ldq, const void* dkv, long ld_dkv, i
                               const int* token_seq, const int* seq_slot, const void* wc, int w_dtype, float eps,
                               const float* cos_sin, int rot_dims, void* q_plain, void* q_full, void* pages,
                               const int* block_table, int table_width, int page_size, int n_tokens, int n_heads,
-                              int plain_dim, int rot_dim, int rank, int write_cache, int* status, void* stream)
+                              int plain_dim, int rot_dim, int rank, int write_cache, int* status, int pairing,
+                              void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (pairing < 0 || pairing > 1) return FX_ERR_SIZE;
     if (rot_dims % 2 || rot_dims > rot_dim || rot_dims < 0 || plain_dim <= 0 || rank <= 0 || page_size <= 0)
         return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
@@ -228,7 +235,7 @@ extern "C" int fx_latent_prep(void* q, long ldq, const void* dkv, long ld_dkv, i
 #define FX_GO(T)                                                                                                      \
     fx_launch_pdl(latent_prep_kernel<T>, n_tokens, nt, 0, s, (T*)q, ldq, (const T*)dkv, ld_dkv, positions,      \
                   token_seq, seq_slot, wc, w_dtype, eps, cos_sin, rot_dims, (T*)q_plain, (T*)q_full, (T*)pages,       \
-                  block_table, table_width, page_size, n_tokens, n_heads, plain_dim, rot_dim, rank, write_cache, status)
+                  block_table, table_width, page_size, n_tokens, n_heads, plain_dim, rot_dim, rank, write_cache, status, pairing)
     if (dtype == FX_F32) FX_GO(float);
     else if (dtype == FX_BF16) FX_GO(bf16);
     else return FX_ERR_DTYPE;
@@ -254,7 +261,7 @@ extern "C" int fx_rmsnorm_rows(const void* x, int x_dtype, long ldx, const void*
 }
 
 extern "C" int fx_heads_to_tokens(const void* in, long in_ldt, long in_ldh, const void* gate, long ldg, void* out, long ldo,
-                                  int dtype, int n_tokens, int n_heads, int width, void* stream)
+                                  int dtype, int n_tokens, int n_heads, int width, int gate_per_head, void* stream)
 {
     if (n_tokens <= 0 || n_heads <= 0 || width <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
@@ -262,10 +269,10 @@ extern "C" int fx_heads_to_tokens(const void* in, long in_ldt, long in_ldh, cons
     if (blocks > fx_sm_count() * 16L) blocks = fx_sm_count() * 16L;
     if (dtype == FX_F32)
         fx_launch_pdl(heads_to_tokens_kernel<float>, (unsigned)blocks, 256, 0, s, (const float*)in, in_ldt, in_ldh, (const float*)gate, ldg,
-                      (float*)out, ldo, n_tokens, n_heads, width);
+                      (float*)out, ldo, n_tokens, n_heads, width, gate_per_head);
     else if (dtype == FX_BF16)
         fx_launch_pdl(heads_to_tokens_kernel<bf16>, (unsigned)blocks, 256, 0, s, (const bf16*)in, in_ldt, in_ldh, (const bf16*)gate, ldg,
-                      (bf16*)out, ldo, n_tokens, n_heads, width);
+                      (bf16*)out, ldo, n_tokens, n_heads, width, gate_per_head);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

@@ -1,0 +1,177 @@
+// What an attention mixer with a short convolution behind its projections does between the fused product and the
+// attention kernel, and what differential attention does after it.
+//
+// fx_conv_rotary_store, one block a token.  The row as projected is [q heads | k heads | v heads]; on every channel
+//
+//   y_t[c] = sum_j w[c, j] u_(t - taps + 1 + j)[c]          (zeros before the request's start; no input added)
+//
+// with the inputs before the step's first token taken from the request's state slot (tail [slots, taps - 1,
+// channels], 32-bit, oldest first: the framework's convention for short convolutions).  Then the first rot_dims
+// elements of every q and k head are turned by the token's angles (cos_sin [tokens][rot_dims / 2][2], which carry
+// any factor on cos and sin; pairs (i, i + rot_dims / 2) or neighbours), q goes to q_out and k and v to the pages
+// (k [pages, k heads, page, head_dim], v [pages, v heads, page, value_dim]).  Sums and rotation are 32-bit; the
+// element type is that of the projected rows.  A step of one token a request (update_tail) also moves the tail on;
+// other steps call fx_conv_tail_update on the projected rows afterwards.
+//
+// fx_diff_combine, one warp a (token, head).  The attention ran over twice as many query heads as the mixer has:
+// for the heads hg = 0 .. group - 1 of kv head g, map j of head g * group + hg is row (2 g + j) * group + hg of the
+// attention's output.  out = rms(a1 - lambda a2) * post over the head's values, without a weight.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv_rotary_store_kernel(
+    const T* __restrict__ proj, long ldp, const void* __restrict__ w, int w_dtype, int taps, float* tail,
+    const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+    const float* __restrict__ cos_sin, int rot_dims, int pairing, T* __restrict__ q_out, long ldq,
+    T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+    int page_size, int n_q_heads, int n_k_heads, int head_dim, int n_v_heads, int value_dim, int write_cache,
+    int update_tail, int* __restrict__ status)
+{
+    fx_pdl_wait();
+    const int t = blockIdx.x;
+    const int b = token_seq[t];
+    const int pos = positions[t];
+    const int slot = seq_slot[b];
+    const int qk = (n_q_heads + n_k_heads) * head_dim, C = qk + n_v_heads * value_dim;
+    // how many rows before t belong to the same entry (at most taps - 1 matter)
+    int own = 0;
+    while (own < taps - 1 && t - own - 1 >= 0 && token_seq[t - own - 1] == b) ++own;
+    float* tl = tail + (long)slot * (taps - 1) * C;
+    const T* row = proj + (long)t * ldp;
+    auto conv = [&](int c) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;
+            float v;
+            if (back <= own) v = to_f32(row[c - (long)back * ldp]);
+            else v = tl[(long)(taps - 1 - (back - own)) * C + c];
+            acc = fmaf(load_any(w, w_dtype, (long)c * taps + j), v, acc);
+        }
+        return acc;
+    };
+    long k_base = -1, v_base = -1;
+    if (write_cache) {
+        const int page = block_table[(long)slot * table_width + pos / page_size];
+        if (page < 0) { if (threadIdx.x == 0 && status) atomicExch(status, 2); }
+        else {
+            k_base = ((long)page * n_k_heads * page_size + (pos % page_size)) * head_dim;
+            v_base = ((long)page * n_v_heads * page_size + (pos % page_size)) * value_dim;
+        }
+    }
+    const int half = rot_dims >> 1;
+    const float* cs = cos_sin ? cos_sin + (long)t * half * 2 : nullptr;
+    // q and k heads: element i of head h; the first of a rotated pair does both, its partner is skipped
+    for (int idx = threadIdx.x; idx < qk; idx += blockDim.x) {
+        const int h = idx / head_dim, i = idx - h * head_dim;
+        float y0, y1 = 0.f;
+        int i0 = i, i1 = -1;
+        if (i < rot_dims && cs) {
+            const int p = pairing ? i >> 1 : i;
+            if (pairing ? (i & 1) : (i >= half)) continue;
+            i1 = pairing ? i + 1 : i + half;
+            const float a = conv(idx), bb = conv(idx - i + i1), c = cs[2 * p], s = cs[2 * p + 1];
+            y0 = a * c - bb * s;
+            y1 = bb * c + a * s;
+        } else {
+            y0 = conv(idx);
+        }
+        if (h < n_q_heads) {
+            T* o = q_out + (long)t * ldq + (long)h * head_dim;
+            o[i0] = from_f32<T>(y0);
+            if (i1 >= 0) o[i1] = from_f32<T>(y1);
+        } else if (k_base >= 0) {
+            T* o = k_pages + k_base + (long)(h - n_q_heads) * page_size * head_dim;
+            o[i0] = from_f32<T>(y0);
+            if (i1 >= 0) o[i1] = from_f32<T>(y1);
+        }
+    }
+    if (v_base >= 0) {
+        for (int idx = threadIdx.x; idx < n_v_heads * value_dim; idx += blockDim.x) {
+            const int h = idx / value_dim, i = idx - h * value_dim;
+            v_pages[v_base + (long)h * page_size * value_dim + i] = from_f32<T>(conv(qk + idx));
+        }
+    }
+    if (update_tail && taps > 1) {
+        // (the caller's promise that every entry brings exactly one token: this block is the only reader of the slot's
+        // tail in the whole step, and moves it on by the token's own row once all its sums are made)
+        __syncthreads();
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            for (int j = 0; j + 1 < taps - 1; ++j) tl[(long)j * C + c] = tl[(long)(j + 1) * C + c];
+            tl[(long)(taps - 2) * C + c] = to_f32(row[c]);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) diff_combine_kernel(const T* __restrict__ attn, long lda, T* __restrict__ out,
+                                                           long ldo, int n_tokens, int n_heads, int group, int V,
+                                                           float lambda, float eps, float post)
+{
+    fx_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= (long)n_tokens * n_heads) return;
+    const int t = (int)(item / n_heads), h = (int)(item - (long)t * n_heads);
+    const int g = h / group, hg = h - g * group;
+    const T* a1 = attn + (long)t * lda + ((long)(2 * g) * group + hg) * V;
+    const T* a2 = attn + (long)t * lda + ((long)(2 * g + 1) * group + hg) * V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) {
+        const float d = to_f32(a1[i]) - lambda * to_f32(a2[i]);
+        ss = fmaf(d, d, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = post / sqrtf(ss / (float)V + eps);
+    T* o = out + (long)t * ldo + (long)h * V;
+    for (int i = lane; i < V; i += 32) o[i] = from_f32<T>((to_f32(a1[i]) - lambda * to_f32(a2[i])) * r);
+}
+
+}  // namespace
+
+extern "C" int fx_conv_rotary_store(const void* proj, int dtype, long ldp, const void* w, int w_dtype, int taps,
+                                    float* tail, const int* positions, const int* token_seq, const int* seq_slot,
+                                    const float* cos_sin, int rot_dims, int pairing, void* q_out, long ldq,
+                                    void* k_pages, void* v_pages, const int* block_table, int table_width,
+                                    int page_size, int n_tokens, int n_q_heads, int n_k_heads, int head_dim,
+                                    int n_v_heads, int value_dim, int write_cache, int update_tail, int* status,
+                                    void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (taps < 1 || taps > MAX_TAPS || rot_dims < 0 || rot_dims % 2 || rot_dims > head_dim || pairing < 0 ||
+        pairing > 1 || page_size <= 0 || head_dim <= 0 || value_dim <= 0 || n_q_heads <= 0 || n_k_heads <= 0 ||
+        n_v_heads <= 0 || proj == q_out)
+        return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+#define FX_GO(T)                                                                                                      \
+    fx_launch_pdl(conv_rotary_store_kernel<T>, n_tokens, 256, 0, s, (const T*)proj, ldp, w, w_dtype, taps, tail,      \
+                  positions, token_seq, seq_slot, cos_sin, rot_dims, pairing, (T*)q_out, ldq, (T*)k_pages,            \
+                  (T*)v_pages, block_table, table_width, page_size, n_q_heads, n_k_heads, head_dim, n_v_heads,        \
+                  value_dim, write_cache, update_tail, status)
+    if (dtype == FX_F32) FX_GO(float);
+    else if (dtype == FX_BF16) FX_GO(bf16);
+    else return FX_ERR_DTYPE;
+#undef FX_GO
+    return fx_launch_status();
+}
+
+extern "C" int fx_diff_combine(const void* attn, long lda, void* out, long ldo, int dtype, int n_tokens, int n_heads,
+                               int group, int value_dim, float lambda, float eps, float post, void* stream)
+{
+    if (n_tokens <= 0) return FX_OK;
+    if (n_heads <= 0 || group <= 0 || n_heads % group || value_dim <= 0) return FX_ERR_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)fx_cdiv((long)n_tokens * n_heads, 4);
+    if (dtype == FX_F32)
+        fx_launch_pdl(diff_combine_kernel<float>, blocks, 128, 0, s, (const float*)attn, lda, (float*)out, ldo,
+                      n_tokens, n_heads, group, value_dim, lambda, eps, post);
+    else if (dtype == FX_BF16)
+        fx_launch_pdl(diff_combine_kernel<bf16>, blocks, 128, 0, s, (const bf16*)attn, lda, (bf16*)out, ldo, n_tokens,
+                      n_heads, group, value_dim, lambda, eps, post);
+    else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}

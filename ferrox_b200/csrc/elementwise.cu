@@ -33,7 +33,7 @@ namespace {
 // A token id outside [0, vocab) writes zeros and raises *status.
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                             int hidden, int vocab, int* __restrict__ status)
+                             int hidden, int vocab, int* __restrict__ status, float scale)
 {
     fx_pdl_wait();
     const int t = blockIdx.x;
@@ -42,7 +42,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
     const T* row = table + (long)(ok ? id : 0) * hidden;
     float* o = out + (long)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;
 }
 
 // ---------------------------------------------------------------------------
@@ -154,7 +154,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long ld, const int* __
 
 // cos_sin[t, i] = (cos, sin)(pos_t * inv_freq[i]), 32-bit angle and functions.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int n_tokens,
-                                  int half, float* __restrict__ cos_sin)
+                                  int half, float* __restrict__ cos_sin, float magnitude)
 {
     fx_pdl_wait();
     const long n = (long)n_tokens * half;
@@ -162,8 +162,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
         const int t = (int)(idx / half), i = (int)(idx - (long)t * half);
         float s, c;
         sincosf((float)positions[t] * inv_freq[i], &s, &c);
-        cos_sin[idx * 2] = c;
-        cos_sin[idx * 2 + 1] = s;
+        cos_sin[idx * 2] = c * magnitude;
+        cos_sin[idx * 2 + 1] = s * magnitude;
     }
 }
 
@@ -493,13 +493,13 @@ __global__ void gather_rows_scaled_kernel(const T* __restrict__ x, long ldx, con
 }  // namespace
 
 extern "C" int fx_embed(const void* table, int dtype, const int* ids, float* out, int n_tokens, int hidden,
-                        int vocab, int* status, void* stream)
+                        int vocab, int* status, float scale, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const int nt = threads_for(hidden > 256 ? 256 : hidden);
-    if (dtype == FX_F32) fx_launch_pdl(embed_kernel<float>, n_tokens, nt, 0, s, (const float*)table, ids, out, hidden, vocab, status);
-    else if (dtype == FX_BF16) fx_launch_pdl(embed_kernel<bf16>, n_tokens, nt, 0, s, (const bf16*)table, ids, out, hidden, vocab, status);
+    if (dtype == FX_F32) fx_launch_pdl(embed_kernel<float>, n_tokens, nt, 0, s, (const float*)table, ids, out, hidden, vocab, status, scale);
+    else if (dtype == FX_BF16) fx_launch_pdl(embed_kernel<bf16>, n_tokens, nt, 0, s, (const bf16*)table, ids, out, hidden, vocab, status, scale);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }
@@ -588,12 +588,12 @@ extern "C" int fx_rope_kv_write(void* qkv, int dtype, long ld, const int* positi
 }
 
 extern "C" int fx_rope_table(const int* positions, const float* inv_freq, int n_tokens, int half, float* cos_sin,
-                             void* stream)
+                             float magnitude, void* stream)
 {
     if (n_tokens <= 0 || half <= 0) return FX_OK;
     long blocks = fx_cdiv((long)n_tokens * half, 128);
     if (blocks > fx_sm_count() * 8L) blocks = fx_sm_count() * 8L;
-    fx_launch_pdl(rope_table_kernel, (unsigned)blocks, 128, 0, (cudaStream_t)stream, positions, inv_freq, n_tokens, half, cos_sin);
+    fx_launch_pdl(rope_table_kernel, (unsigned)blocks, 128, 0, (cudaStream_t)stream, positions, inv_freq, n_tokens, half, cos_sin, magnitude);
     return fx_launch_status();
 }
 
@@ -686,6 +686,59 @@ extern "C" int fx_gather_rows(const void* x, long ldx, const int* rows, void* ou
     else if (dtype == FX_BF16)
         fx_launch_pdl(gather_rows_kernel<bf16>, n_rows, 128, 0, s, (const bf16*)x, ldx, rows, (bf16*)out, ldo, width, vec_ok);
     else return FX_ERR_DTYPE;
+    return fx_launch_status();
+}
+
+// h[r, :] += scale * y[r, :] in 32 bits and, with a weight, x_out[r, :] = h[r, :] / sqrt(mean(h[r, :]^2) + eps) * w on
+// the new row: the residual addition of a block whose sublayers' sum is multiplied by a constant, with the norm that
+// the next block starts with.  One block a row; the new row stays in registers between the two passes.
+template <typename OT, int PER>
+__global__ void __launch_bounds__(256) scaled_add_norm_kernel(float* __restrict__ h, const float* __restrict__ y,
+                                                              float scale, const void* __restrict__ w, int w_dtype,
+                                                              float eps, OT* __restrict__ x_out, int hidden)
+{
+    __shared__ float scratch[33];
+    fx_pdl_wait();
+    float* hr = h + (long)blockIdx.x * hidden;
+    const float* yr = y + (long)blockIdx.x * hidden;
+    float v[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = 0.f;
+        if (i < hidden) { v[j] = fmaf(scale, yr[i], hr[i]); hr[i] = v[j]; ss = fmaf(v[j], v[j], ss); }
+    }
+    if (!w) return;      // (uniform)
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+    OT* o = x_out + (long)blockIdx.x * hidden;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < hidden) o[i] = from_f32<OT>(v[j] * r * load_any(w, w_dtype, i));
+    }
+}
+
+extern "C" int fx_scaled_add_norm(float* h, const float* y, float scale, const void* w, int w_dtype, float eps,
+                                  void* x_out, int x_dtype, int n_rows, int hidden, void* stream)
+{
+    if (n_rows <= 0 || hidden <= 0) return FX_OK;
+    if (hidden > 32 * 256) return FX_ERR_SIZE;
+    if (w && x_dtype != FX_F32 && x_dtype != FX_BF16) return FX_ERR_DTYPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int per = (int)fx_cdiv(hidden, 256);
+#define FX_GO(OT, PER)                                                                                               \
+    fx_launch_pdl(scaled_add_norm_kernel<OT, PER>, n_rows, 256, 0, s, h, y, scale, w, w_dtype, eps, (OT*)x_out, hidden)
+#define FX_PICK(OT)                                                                                                  \
+    do {                                                                                                             \
+        if (per <= 1) FX_GO(OT, 1); else if (per <= 2) FX_GO(OT, 2); else if (per <= 4) FX_GO(OT, 4);                \
+        else if (per <= 8) FX_GO(OT, 8); else if (per <= 16) FX_GO(OT, 16); else FX_GO(OT, 32);                      \
+    } while (0)
+    if (w && x_dtype == FX_BF16) FX_PICK(bf16);
+    else FX_PICK(float);
+#undef FX_PICK
+#undef FX_GO
     return fx_launch_status();
 }
 

@@ -2,6 +2,9 @@
 //
 //   out[t, c] = x[t, c] + sum_j w[c, j] * x[t - (taps - 1) + j, c]        (zeros before the request's start)
 //
+// (add_input = 0: the sum alone, for a convolution that stands in its input's place, as the one behind the
+// projections of an attention mixer)
+//
 // over the tokens of one request.  The taps - 1 inputs before a step's first token come from the request's state
 // slot (`tail` [slots, taps - 1, channels], 32-bit, oldest first), so a request may be cut into steps anywhere;
 // after the step the last taps - 1 inputs of every entry become its tail (fx_conv_tail_update, linear_state.cu; a
@@ -21,7 +24,7 @@ template <typename T>
 __global__ void __launch_bounds__(CONV_THREADS) input_conv_kernel(
     const T* __restrict__ x, long ldx, const void* __restrict__ w, int w_dtype, int taps, float* tail,
     const int* __restrict__ token_seq, const int* __restrict__ seq_slot, T* __restrict__ out, long ldo, int C,
-    int update_tail)
+    int update_tail, int add_input)
 {
     fx_pdl_wait();
     const int t = blockIdx.x;
@@ -33,7 +36,7 @@ __global__ void __launch_bounds__(CONV_THREADS) input_conv_kernel(
     while (own < taps - 1 && t - own - 1 >= 0 && token_seq[t - own - 1] == b) ++own;
     float* tl = tail + (long)seq_slot[b] * (taps - 1) * C;
     const float xt = to_f32(x[(long)t * ldx + c]);
-    float acc = xt;
+    float acc = add_input ? xt : 0.f;     // (a convolution that replaces its input: the sum alone)
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;          // this tap's input lies `back` tokens before t
         float v;
@@ -94,7 +97,7 @@ __global__ void relu_square_kernel(T* __restrict__ x, long ld, int n)
 
 extern "C" int fx_input_conv(const void* x, int dtype, long ldx, const void* w, int w_dtype, int taps, float* tail,
                              const int* token_seq, const int* seq_slot, void* out, long ldo, int n_tokens, int channels,
-                             int update_tail, void* stream)
+                             int update_tail, int add_input, void* stream)
 {
     if (n_tokens <= 0 || channels <= 0) return FX_OK;
     if (taps < 1 || taps > CONV_MAX_TAPS || x == out) return FX_ERR_SIZE;
@@ -102,10 +105,10 @@ extern "C" int fx_input_conv(const void* x, int dtype, long ldx, const void* w, 
     dim3 grid(n_tokens, (unsigned)fx_cdiv(channels, CONV_THREADS));
     if (dtype == FX_F32)
         fx_launch_pdl(input_conv_kernel<float>, grid, CONV_THREADS, 0, s, (const float*)x, ldx, w, w_dtype, taps, tail,
-                      token_seq, seq_slot, (float*)out, ldo, channels, update_tail);
+                      token_seq, seq_slot, (float*)out, ldo, channels, update_tail, add_input);
     else if (dtype == FX_BF16)
         fx_launch_pdl(input_conv_kernel<bf16>, grid, CONV_THREADS, 0, s, (const bf16*)x, ldx, w, w_dtype, taps, tail,
-                      token_seq, seq_slot, (bf16*)out, ldo, channels, update_tail);
+                      token_seq, seq_slot, (bf16*)out, ldo, channels, update_tail, add_input);
     else return FX_ERR_DTYPE;
     return fx_launch_status();
 }

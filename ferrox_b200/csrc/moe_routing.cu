@@ -6,6 +6,20 @@
 
 namespace {
 
+// What a router may ask for beside the mode: a number per expert added to the score for the CHOICE only (the weights
+// use the scores without it; with the sigmoid scores of mode bit 1), a factor on the final weights, and a small
+// number added to the sum the kept scores are divided by.
+struct RouteExtra {
+    const float* choice_bias;
+    float weight_scale, renorm_eps;
+};
+
+// a float's bit pattern as an unsigned number that orders like the float (negative values included), never zero
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
 // One warp per token.  p = softmax(logits) over ALL experts (max-subtracted), the k
 // largest p are kept in descending order, on equal p the lowest expert index wins,
 // and the weights are the kept p, divided by their sum when bit 0 of `renorm` is set.  Bit 1 of `renorm`: the
@@ -17,14 +31,20 @@ namespace {
 // warp reductions instead of two chains of shuffles.  `counts` (optional): counts[e] += 1 for each kept expert.
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, float* p, int lane, int t, int n_experts,
                                             int top_k, int renorm, int* __restrict__ ids, float* __restrict__ weights,
-                                            int* __restrict__ counts = nullptr, int* ids_shared = nullptr)
+                                            const RouteExtra x, int* __restrict__ counts = nullptr,
+                                            int* ids_shared = nullptr)
 {
     uint32_t* pb = reinterpret_cast<uint32_t*>(p);
     float mx = -INFINITY;
     for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) { const float v = expf(lg[e] - mx); pb[e] = __float_as_uint(v) + 1u; sum += v; }
+    if (x.choice_bias) {
+        // the choice is made on sigmoid(logit) + bias[e], which may be negative: patterns that order like the values
+        for (int e = lane; e < n_experts; e += 32) pb[e] = ordered_bits(1.0f / (1.0f + expf(-lg[e])) + x.choice_bias[e]);
+    } else {
+        for (int e = lane; e < n_experts; e += 32) { const float v = expf(lg[e] - mx); pb[e] = __float_as_uint(v) + 1u; sum += v; }
+    }
     sum = warp_sum(sum);
     __syncwarp();
     // up to 32 kept experts stay in registers (lane k holds the k-th) and are written once, side by side
@@ -55,18 +75,22 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
     if (in_regs) {
         if (lane < top_k) {
             ids[(long)t * top_k + lane] = mine_e;
-            weights[(long)t * top_k + lane] = (renorm & 1) ? mine_w / kept : mine_w;
+            weights[(long)t * top_k + lane] = ((renorm & 1) ? mine_w / (kept + x.renorm_eps) : mine_w) * x.weight_scale;
             if (ids_shared) ids_shared[t * top_k + lane] = mine_e;
             if (counts) atomicAdd(&counts[mine_e], 1);
         }
-    } else if (renorm & 1) {
+    } else if ((renorm & 1) || x.weight_scale != 1.0f) {
         __syncwarp();
-        for (int k = lane; k < top_k; k += 32) weights[(long)t * top_k + k] /= kept;
+        for (int k = lane; k < top_k; k += 32) {
+            const float w = weights[(long)t * top_k + k];
+            weights[(long)t * top_k + k] = ((renorm & 1) ? w / (kept + x.renorm_eps) : w) * x.weight_scale;
+        }
     }
 }
 
 __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k,
-                                   int renorm, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts)
+                                   int renorm, int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts,
+                                   const RouteExtra x)
 {
     extern __shared__ float smem[];  // [warps][n_experts]
     fx_pdl_wait();
@@ -74,7 +98,7 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, in
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= n_tokens) return;
     route_token(logits + (long)t * ld, smem + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
-                weights, counts);
+                weights, x, counts);
 }
 
 // Routing and bookkeeping of a small step in ONE block: top-k per token (a warp
@@ -86,7 +110,7 @@ __device__ __forceinline__ void route_in_block(const float* lg, long ld, float* 
                                                int* __restrict__ ids, float* __restrict__ weights,
                                                int* __restrict__ offsets, int* __restrict__ src_token,
                                                int* __restrict__ inv_perm, int* __restrict__ active, int n_slots,
-                                               int* ids_s = nullptr, int* src_s = nullptr)
+                                               const RouteExtra x, int* ids_s = nullptr, int* src_s = nullptr)
 {
     // ids_s, src_s (optional, shared memory, n_tokens * top_k ints each): the block keeps what it chose and where it
     // put it beside the copies in global memory, so that it (and its caller) need not read those back
@@ -96,7 +120,7 @@ __device__ __forceinline__ void route_in_block(const float* lg, long ld, float* 
     __syncthreads();
     for (int t = warp; t < n_tokens; t += n_warps) {
         route_token(lg + (long)t * ld, p_scratch + (long)warp * n_experts, lane, t, n_experts, top_k, renorm, ids,
-                    weights, counts, ids_s);
+                    weights, x, counts, ids_s);
         __syncwarp();
     }
     __syncthreads();  // ids written by this block are visible to it after the barrier
@@ -138,13 +162,13 @@ constexpr int SMALL_WARPS = 32;
 __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
     const float* __restrict__ logits, long ld, int n_tokens, int n_experts, int top_k, int renorm,
     int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ offsets, int* __restrict__ src_token, int* __restrict__ inv_perm,
-    int* __restrict__ active, int n_slots)
+    int* __restrict__ active, int n_slots, const RouteExtra x)
 {
     extern __shared__ float smem[];  // [SMALL_WARPS][n_experts] floats, then 2 * n_experts + 1 ints
     fx_pdl_wait();
     int* counts = reinterpret_cast<int*>(smem + (long)SMALL_WARPS * n_experts);
     route_in_block(logits, ld, smem, counts, SMALL_WARPS, n_tokens, n_experts, top_k, renorm, ids, weights, offsets,
-                   src_token, inv_perm, active, n_slots);
+                   src_token, inv_perm, active, n_slots, x);
 }
 
 // What stands between the norm and the experts in a decode step of a few tokens, in ONE launch of one cluster of
@@ -164,6 +188,7 @@ struct FusedArgs {
     float* logits_out; long ldl;
     int* ids; float* weights; int* offsets; int* src_token; int* inv_perm; int* active; int n_slots;
     bf16* xp_out; long ldxp;                 // rows in expert order (may be null)
+    RouteExtra extra;
 };
 
 constexpr int FUSED_CTAS = 8, FUSED_WARPS = 8, FUSED_PASS = 8;   // a pass: 8 x 16 bytes a lane = 2,048 elements a warp
@@ -248,7 +273,7 @@ __global__ void __launch_bounds__(FUSED_WARPS * 32) route_fused_kernel(FusedArgs
     int* ids_s = counts + 2 * a.n_experts + 1;      // [NT * top_k], then src_s [NT * top_k]
     int* src_s = ids_s + NT * a.top_k;
     route_in_block(lg_s, n_route, p_scratch, counts, FUSED_WARPS, n_tokens, a.n_experts, a.top_k, a.renorm, a.ids, a.weights,
-                   a.offsets, a.src_token, a.inv_perm, a.active, a.n_slots, ids_s, src_s);
+                   a.offsets, a.src_token, a.inv_perm, a.active, a.n_slots, a.extra, ids_s, src_s);
     if (a.xp_out) {
         // the rows in expert order, out of shared memory: a warp a row, 16 bytes a lane and pass
         __syncthreads();
@@ -363,16 +388,24 @@ __global__ void scan_place_kernel(const int* __restrict__ ids, int n, int n_expe
 
 }  // namespace
 
-extern "C" int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
-                              float* weights, void* stream)
+static RouteExtra route_extra(const float* choice_bias, float weight_scale, float renorm_eps)
 {
+    RouteExtra x;
+    x.choice_bias = choice_bias; x.weight_scale = weight_scale; x.renorm_eps = renorm_eps;
+    return x;
+}
+
+extern "C" int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
+                              float* weights, const float* choice_bias, float weight_scale, float renorm_eps, void* stream)
+{
+    if (choice_bias && !(renorm & 2)) return FX_ERR_SIZE;      // (the choice bias goes with the sigmoid scores)
     if (n_tokens <= 0) return FX_OK;
     if (top_k <= 0 || top_k > n_experts || n_experts > 4096) return FX_ERR_SIZE;
     const int warps = 4;
     const size_t smem = (size_t)warps * n_experts * sizeof(float);
     if (smem > 48 * 1024) return FX_ERR_SIZE;
     router_topk_kernel<<<(unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, (cudaStream_t)stream>>>(
-        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, nullptr);
+        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, nullptr, route_extra(choice_bias, weight_scale, renorm_eps));
     return fx_launch_status();
 }
 
@@ -380,9 +413,10 @@ extern "C" int fx_router_topk(const float* logits, long ld, int n_tokens, int n_
 // rows of every expert as it chooses them, the placing kernel sums the counts itself.  scratch: 2 * n_experts ints.
 extern "C" int fx_route(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
                         float* weights, int* scratch, int* offsets, int* src_token, int* inv_perm, int* active,
-                        int n_slots, void* stream)
+                        int n_slots, const float* choice_bias, float weight_scale, float renorm_eps, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (choice_bias && !(renorm & 2)) return FX_ERR_SIZE;
     if (top_k <= 0 || top_k > n_experts || n_experts > SCAN_MAX_EXPERTS) return FX_ERR_SIZE;
     const int warps = 4;
     const size_t smem = (size_t)warps * n_experts * sizeof(float);
@@ -391,7 +425,8 @@ extern "C" int fx_route(const float* logits, long ld, int n_tokens, int n_expert
     cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int) * 2 * n_experts, s);
     if (e != cudaSuccess) return (int)e;
     fx_launch_pdl(router_topk_kernel, (unsigned)fx_cdiv(n_tokens, warps), warps * 32, smem, s,
-                  logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, scratch);
+                  logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, scratch,
+                  route_extra(choice_bias, weight_scale, renorm_eps));
     const int n = n_tokens * top_k;
     int blocks = (int)fx_cdiv(n, 256);
     if (blocks > fx_sm_count() * 4L) blocks = fx_sm_count() * 4L;
@@ -403,14 +438,16 @@ extern "C" int fx_route(const float* logits, long ld, int n_tokens, int n_expert
 // Routing of at most 1024 tokens in one launch (see route_small_kernel).
 extern "C" int fx_route_small(const float* logits, long ld, int n_tokens, int n_experts, int top_k, int renorm, int* ids,
                               float* weights, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots,
-                              void* stream)
+                              const float* choice_bias, float weight_scale, float renorm_eps, void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (choice_bias && !(renorm & 2)) return FX_ERR_SIZE;
     if (top_k <= 0 || top_k > n_experts || n_tokens > 1024) return FX_ERR_SIZE;
     const size_t smem = (size_t)SMALL_WARPS * n_experts * sizeof(float) + (2 * (size_t)n_experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return FX_ERR_SIZE;
     fx_launch_pdl(route_small_kernel, 1, SMALL_WARPS * 32, smem, (cudaStream_t)stream,
-        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots);
+        logits, ld, n_tokens, n_experts, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active, n_slots,
+        route_extra(choice_bias, weight_scale, renorm_eps));
     return fx_launch_status();
 }
 
@@ -446,9 +483,11 @@ static int launch_route_fused(size_t smem, cudaStream_t s, const FusedArgs& a)
 extern "C" int fx_route_fused(const void* X, long ldx, const void* W, long ldw, int n_tokens, int n_route,
                               int n_experts, int hidden, int top_k, int renorm, float* logits, long ldl, int* ids,
                               float* weights, int* offsets, int* src_token, int* inv_perm, int* active, int n_slots,
-                              void* xp_out, long ldxp, void* stream)
+                              void* xp_out, long ldxp, const float* choice_bias, float weight_scale, float renorm_eps,
+                              void* stream)
 {
     if (n_tokens <= 0) return FX_OK;
+    if (choice_bias && !(renorm & 2)) return FX_ERR_SIZE;
     if (n_tokens > 8 || top_k <= 0 || top_k > n_experts || top_k > 64 || n_experts > n_route || n_route > 1024 || hidden <= 0)
         return FX_ERR_SIZE;
     if (hidden % 8 || ldw % 8 || (uintptr_t)W % 16 || ldx % 8 || (uintptr_t)X % 16) return FX_ERR_ALIGN;
@@ -462,6 +501,7 @@ extern "C" int fx_route_fused(const void* X, long ldx, const void* W, long ldw, 
     a.n_tokens = n_tokens; a.n_route = n_route; a.n_experts = n_experts; a.hidden = hidden; a.top_k = top_k; a.renorm = renorm;
     a.logits_out = logits; a.ldl = ldl; a.ids = ids; a.weights = weights; a.offsets = offsets; a.src_token = src_token;
     a.inv_perm = inv_perm; a.active = active; a.n_slots = n_slots; a.xp_out = (bf16*)xp_out; a.ldxp = ldxp;
+    a.extra = route_extra(choice_bias, weight_scale, renorm_eps);
     cudaStream_t s = (cudaStream_t)stream;
     switch (nt) {
         case 1: return launch_route_fused<1>(smem, s, a);

@@ -36,11 +36,12 @@ _SIGNATURES = {
     "fx_set_pdl": [_I],
     "fx_set_scan_lanes": [_I],
     "fx_gemm": [_P, _I, _L, _P, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _I, _L, _P],
-    "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _P],
+    "fx_embed": [_P, _I, _P, _P, _I, _I, _I, _P, _F, _P],
+    "fx_scaled_add_norm": [_P, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _I, _I, _P],
     "fx_silu_mul": [_P, _L, _P, _L, _I, _P, _I, _I, _P],
     "fx_rope_kv_write": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
-    "fx_rope_table": [_P, _P, _I, _I, _P, _P],
+    "fx_rope_table": [_P, _P, _I, _I, _P, _F, _P],
     "fx_gemm_tc": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _P, _P],
     "fx_gemm_tc_swap": [_P, _L, _P, _L, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _F, _F, _P, _I, _I, _I, _I, _P, _P,
                         _P],
@@ -48,19 +49,19 @@ _SIGNATURES = {
     "fx_gather_rows": [_P, _L, _P, _P, _L, _I, _I, _I, _P],
     "fx_gather_rows_scaled": [_P, _L, _P, _P, _P, _I, _P, _L, _I, _I, _I, _P],
     "fx_paged_attention_ex": [_P, _L, _L, _P, _P, _L, _L, _I, _P, _I, _I, _P, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _I, _F,
-                              _F, _P, _I, _P],
+                              _F, _P, _I, _P, _I, _P],
     "fx_general_attention_ok": [_I, _I, _I],
     "fx_general_attention": [_P, _L, _L, _P, _P, _L, _L, _P, _P, _I, _I, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I,
-                             _F, _P, _I, _P, _P, _I, _P],
+                             _F, _P, _I, _P, _P, _I, _F, _P, _I, _P],
     "fx_qk_norm_store": [_P, _I, _L, _P, _P, _P, _P, _P, _I, _F, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _F,
                          _P],
     "fx_latent_prep": [_P, _L, _P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P,
-                       _P],
+                       _I, _P],
     "fx_rmsnorm_rows": [_P, _I, _L, _P, _I, _F, _P, _I, _L, _I, _I, _P],
-    "fx_heads_to_tokens": [_P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _I, _P],
-    "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P],
-    "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
-    "fx_route_fused": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P],
+    "fx_heads_to_tokens": [_P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
+    "fx_route_small": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _P],
+    "fx_route": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _P],
+    "fx_route_fused": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P, _F, _F, _P],
     "fx_moe_combine": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P],
     "fx_moe_combine_norm": [_P, _P, _I, _P, _P, _I, _P, _P, _L, _I, _I, _P, _I, _F, _P, _P],
     "fx_residual_add": [_P, _P, _I, _L, _P],
@@ -75,14 +76,20 @@ _SIGNATURES = {
     "fx_gated_group_norm": [_P, _P, _I, _L, _P, _I, _F, _I, _P, _I, _I, _I, _I, _L, _P],
     "fx_general_delta_prep": [_P, _L, _P, _L, _P, _L, _P, _I, _P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _P],
     "fx_general_delta_scan": [_P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _P],
-    "fx_input_conv": [_P, _I, _L, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _P],
+    "fx_input_conv": [_P, _I, _L, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
+    "fx_mlstm_column_blocks": [_I, _I],
+    "fx_mlstm_scan": [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _I, _F, _F, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I,
+                      _P],
+    "fx_conv_rotary_store": [_P, _I, _L, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                             _I, _I, _I, _I, _P, _P],
+    "fx_diff_combine": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _F, _F, _F, _P],
     "fx_embed_pos": [_P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     "fx_softcap": [_P, _L, _F, _P],
     "fx_relu_square": [_P, _I, _L, _I, _I, _P],
     "fx_prefill_attention": [_P, _L, _P, _P, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _F, _P],
     "fx_prefill_attention_tc": [_P, _L, _I, _P, _P, _I, _P, _I, _I, _P, _I, _P, _P, _L, _I, _I, _I, _I, _F, _P, _P, _P,
                                 _P, _I, _P],
-    "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P],
+    "fx_router_topk": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _F, _F, _P],
     "fx_moe_align": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "fx_gemm_slab_ok": [_I, _I, _I],
     "fx_gemm_slab": [_P, _L, _P, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P, _P],
@@ -288,9 +295,22 @@ def gemm(a, w, out, *, bias=None, accumulate=False, a_rows=None, group_offsets=N
     return out
 
 
-def embed(table, ids, out, status=None, stream=None):
+def embed(table, ids, out, status=None, stream=None, scale=1.0):
+    """out[t] = table[ids[t]] * scale in 32 bits."""
     T = ids.numel()
     call("fx_embed", _ptr(table), code(table), _ptr(ids), _ptr(out), T, table.shape[1], table.shape[0], _ptr(status),
+         float(scale), stream if stream is not None else stream_ptr())
+    return out
+
+
+def scaled_add_norm(h, y, scale, norm=None, stream=None):
+    """h += scale * y over the 32-bit rows of the residual stream; ``norm`` = (weight, eps, out): also out = h /
+    sqrt(mean(h^2) + eps) * weight on the new rows, in the same kernel.  Returns ``out`` (None without a norm)."""
+    if h.dtype != torch.float32 or y.dtype != torch.float32 or h.shape != y.shape or not (h.is_contiguous() and y.is_contiguous()):
+        raise KernelError("scaled_add_norm: two contiguous 32-bit tensors of one shape")
+    w, eps, out = norm if norm is not None else (None, 0.0, None)
+    call("fx_scaled_add_norm", _ptr(h), _ptr(y), float(scale), _ptr(w), code(w) if w is not None else 0, float(eps),
+         _ptr(out), code(out) if out is not None else 0, h.shape[0], h.shape[1],
          stream if stream is not None else stream_ptr())
     return out
 
@@ -479,15 +499,77 @@ def general_delta_scan(r, k, v, u, au, w, state, out, token_seq, seq_slot, n_ent
     return out
 
 
-def input_conv(x, weight, taps, tail, token_seq, seq_slot, out, update_tail=False, stream=None):
+def mlstm_column_blocks(head_dim: int, value_dim: int) -> int:
+    """Blocks of value columns :func:`mlstm_scan` shares a head's state out over: the copies of the normaliser and of
+    the running maximum that the state keeps.  A function of the two sizes alone, stated here as the kernel's
+    launcher states it (128 threads a block; 4 lanes a column, doubled while a lane would hold more than 32 rows), so
+    that a cache can be laid out without the library; the launcher refuses a state laid out otherwise."""
+    D, V = int(head_dim), int(value_dim)
+    if not (0 < D <= 512 and V > 0):
+        raise KernelError(f"mlstm: heads of {head_dim} x {value_dim} are outside what the recurrence kernel holds")
+    lanes = 4
+    while lanes < 32 and -(-D // lanes) > 32:
+        lanes *= 2
+    cols = 128 // lanes
+    return -(-V // cols)
+
+
+def mlstm_scan(q, k, v, gates, i_bias, f_bias, cap, q_scale, matrix, normalizer, log_max, out, token_seq, seq_slot,
+               n_entries, H, D, V, stream=None):
+    """The mLSTM recurrence over every entry's tokens in order (see csrc/mlstm.cu).  ``q``, ``k`` [T, H*D], ``v``
+    [T, H*V] and ``gates`` [T, >= 2H] (input gates' then forget gates' pre-activations) are 32-bit row views;
+    ``matrix`` [slots, H, V, D], ``normalizer`` [slots, H, Z, D] and ``log_max`` [slots, H, Z] the requests' states
+    (Z = :func:`mlstm_column_blocks`); ``out`` [T, H*V] 32-bit."""
+    for t in (q, k, v, gates, out, matrix, normalizer, log_max):
+        if t.dtype != torch.float32:
+            raise KernelError("mlstm_scan: 32-bit rows and states")
+    if i_bias.dtype != f_bias.dtype:
+        raise KernelError("mlstm_scan: both gate biases of one element type")
+    call("fx_mlstm_scan", _ptr(q), _rows(q), _ptr(k), _rows(k), _ptr(v), _rows(v), _ptr(gates), _rows(gates), _ptr(i_bias),
+         _ptr(f_bias), code(i_bias), float(cap), float(q_scale), _ptr(matrix), _ptr(normalizer), _ptr(log_max), _ptr(out),
+         _rows(out), _ptr(token_seq), _ptr(seq_slot), q.shape[0], int(n_entries), H, D, V, int(normalizer.shape[2]),
+         stream if stream is not None else stream_ptr())
+    return out
+
+
+def conv_rotary_store(proj, weight, taps, tail, positions, token_seq, seq_slot, cos_sin, rot_dims, pairing, q_out,
+                      k_pages, v_pages, block_table, page_size, n_q_heads, n_k_heads, head_dim, n_v_heads, value_dim,
+                      write_cache=True, update_tail=False, status=None, stream=None):
+    """Rows of [q heads | k heads | v heads] as projected: a short causal convolution on every channel (``weight``
+    [channels, taps], nothing added; the inputs before the step from ``tail`` [slots, taps - 1, channels] 32-bit),
+    the first ``rot_dims`` elements of every q and k head turned by ``cos_sin`` [T, rot_dims / 2, 2] (None: no
+    rotation), q into ``q_out`` [T, n_q_heads * head_dim], k and v into their pages ([pages, n_k_heads, page,
+    head_dim], [pages, n_v_heads, page, value_dim]).  ``update_tail``: only when every entry brings exactly one
+    token; the kernel then moves the tail on (:func:`conv_tail_update` on ``proj`` otherwise)."""
+    if q_out.dtype != proj.dtype or k_pages.dtype != proj.dtype or v_pages.dtype != proj.dtype:
+        raise KernelError("conv_rotary_store: rows, queries and pages of one element type")
+    call("fx_conv_rotary_store", _ptr(proj), code(proj), _rows(proj), _ptr(weight), code(weight), int(taps), _ptr(tail),
+         _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(cos_sin), int(rot_dims if cos_sin is not None else 0),
+         int(pairing), _ptr(q_out), _rows(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+         page_size, proj.shape[0], n_q_heads, n_k_heads, head_dim, n_v_heads, value_dim, int(write_cache),
+         int(update_tail), _ptr(status), stream if stream is not None else stream_ptr())
+    return q_out
+
+
+def diff_combine(attn, out, n_heads, group, value_dim, lam, eps, post, stream=None):
+    """out[t, h] = rms(a1 - lam * a2) * post per head, without a weight: the two maps of head h = g * group + hg are
+    rows (2 g) * group + hg and (2 g + 1) * group + hg of ``attn`` [T, 2 * n_heads * value_dim]."""
+    if attn.dtype != out.dtype:
+        raise KernelError("diff_combine: one element type")
+    call("fx_diff_combine", _ptr(attn), _rows(attn), _ptr(out), _rows(out), code(attn), attn.shape[0], n_heads, group,
+         value_dim, float(lam), float(eps), float(post), stream if stream is not None else stream_ptr())
+    return out
+
+
+def input_conv(x, weight, taps, tail, token_seq, seq_slot, out, update_tail=False, stream=None, add_input=True):
     """out[t] = x[t] + sum_j weight[:, j] x[t - taps + 1 + j] over the tokens of each request (``weight`` [channels,
     taps]); the inputs before the step come from ``tail`` [slots, taps - 1, channels] 32-bit.  ``update_tail``: only
     when every entry brings exactly one token; the kernel then also moves the tail on (:func:`conv_tail_update`
-    otherwise)."""
+    otherwise).  ``add_input`` False: the sum alone."""
     if out.dtype != x.dtype or out.data_ptr() == x.data_ptr():
         raise KernelError("input_conv: an output of its own, of the input's element type")
     call("fx_input_conv", _ptr(x), code(x), _rows(x), _ptr(weight), code(weight), int(taps), _ptr(tail), _ptr(token_seq),
-         _ptr(seq_slot), _ptr(out), _rows(out), x.shape[0], x.shape[1], int(update_tail),
+         _ptr(seq_slot), _ptr(out), _rows(out), x.shape[0], x.shape[1], int(update_tail), int(add_input),
          stream if stream is not None else stream_ptr())
     return out
 
@@ -514,20 +596,30 @@ def relu_square_(x, stream=None):
     return x
 
 
-def rope_table(positions, inv_freq, out, stream=None):
-    """out[t, i] = (cos, sin)(positions[t] * inv_freq[i]); out is float32 [T, half, 2]."""
+def rope_table(positions, inv_freq, out, stream=None, magnitude=1.0):
+    """out[t, i] = magnitude * (cos, sin)(positions[t] * inv_freq[i]); out is float32 [T, half, 2]."""
     call("fx_rope_table", _ptr(positions), _ptr(inv_freq), positions.numel(), inv_freq.numel(), _ptr(out),
-         stream if stream is not None else stream_ptr())
+         float(magnitude), stream if stream is not None else stream_ptr())
     return out
 
 
+def _route_extra(extra):
+    """(choice bias pointer, weight scale, renorm eps) of the routing entry points; ``extra`` None: none of them."""
+    bias, scale, eps = extra if extra is not None else (None, 1.0, 0.0)
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous()):
+        raise KernelError("routing: the choice bias is a contiguous 32-bit vector, one number per expert")
+    return _ptr(bias), float(scale), float(eps)
+
+
 def route_small(logits, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active=None, n_experts=None,
-                stream=None):
-    """router_topk and moe_align of a small step (at most 1024 tokens) in one launch."""
+                stream=None, extra=None):
+    """router_topk and moe_align of a small step (at most 1024 tokens) in one launch.  ``extra`` = (choice_bias,
+    weight_scale, renorm_eps): a 32-bit number per expert added to sigmoid(logit) for the choice only, a factor on
+    the final weights, a number added to the sum the kept scores are divided by (all four routing calls take it)."""
     T, E = logits.shape[0], (n_experts or logits.shape[1])
     call("fx_route_small", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(offsets),
          _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
-         stream if stream is not None else stream_ptr())
+         *_route_extra(extra), stream if stream is not None else stream_ptr())
 
 
 ROUTE_FUSED_MAX_TOKENS = 8     # the kernel keeps a sum per token in registers
@@ -546,7 +638,7 @@ def route_fused_ok(x, w_route, n_experts: int, top_k: int = 1) -> bool:
 
 
 def route_fused(x, w_route, logits, top_k, renorm, ids, weights, offsets, src_token, inv_perm, active=None, n_experts=None,
-                xp_out=None, stream=None):
+                xp_out=None, stream=None, extra=None):
     """What stands between the norm and the experts in a step of a few tokens, in one launch of one thread-block
     cluster (see :func:`route_fused_ok`): the router's product logits = x . w_route^T (32-bit sums; ``w_route`` may carry
     rows beyond the experts', whose logits later kernels read), :func:`route_small` on the first ``n_experts`` columns
@@ -558,7 +650,7 @@ def route_fused(x, w_route, logits, top_k, renorm, ids, weights, offsets, src_to
     call("fx_route_fused", _ptr(x), _rows(x), _ptr(w_route), _rows(w_route), T, R, E, H, top_k, int(renorm), _ptr(logits),
          _rows(logits), _ptr(ids), _ptr(weights), _ptr(offsets), _ptr(src_token), _ptr(inv_perm), _ptr(active),
          active.numel() if active is not None else 0, _ptr(xp_out), _rows(xp_out) if xp_out is not None else 0,
-         stream if stream is not None else stream_ptr())
+         *_route_extra(extra), stream if stream is not None else stream_ptr())
 
 
 ROUTE_SMALL_MAX_TOKENS = 48    # measured with 60 experts: the one-block kernel 4 to 8 us up to here, the two kernels 8 us
@@ -566,13 +658,13 @@ ROUTE_SMALL_MAX_EXPERTS = 256  # its shared memory: 32 warps x experts x 4 bytes
 
 
 def route(logits, top_k, renorm, ids, weights, scratch, offsets, src_token, inv_perm, active=None, n_experts=None,
-          stream=None):
+          stream=None, extra=None):
     """router_topk and moe_align of a step of any size: the top-k kernel counts each expert's rows as it chooses,
     the placing kernel sums the counts itself.  ``scratch``: 2 * n_experts int32."""
     T, E = logits.shape[0], (n_experts or logits.shape[1])
     call("fx_route", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights), _ptr(scratch),
          _ptr(offsets), _ptr(src_token), _ptr(inv_perm), _ptr(active), active.numel() if active is not None else 0,
-         stream if stream is not None else stream_ptr())
+         *_route_extra(extra), stream if stream is not None else stream_ptr())
 
 
 PAIR_HALVES, PAIR_ADJACENT = 0, 1
@@ -606,20 +698,25 @@ def paged_attention(q, k_pages, v_pages, block_table, page_size, positions, toke
 
 def paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
                        out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, softcap=None, slopes=None,
-                       stream=None, keep_first=0):
+                       stream=None, keep_first=0, sinks=None, value_share=1):
     """:func:`paged_attention` in its general form: keys of ``key_dim`` and values of ``value_dim`` elements whose
     positions lie ``ldk`` / ``ldv`` elements apart in their pages (values that are the leading part of the cached
     key rows: the same tensor twice with ldv = ldk); ``q`` and ``out`` are any tensors addressed by a token stride
     and a head stride; ``slopes`` (float32 [n_heads], optional): slopes[h] * (i - j) is taken off the score of key j
     for the query at position i; ``keep_first`` (with a window): the request's first positions stay visible beside
-    the window."""
+    the window; ``sinks`` (float32 [n_heads], optional): exp(sinks[h]) joins the softmax's denominator once;
+    ``value_share``: that many consecutive key heads read one value head (the value pages hold n_kv_heads /
+    value_share heads)."""
     T = positions.numel()
     if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != n_heads):
         raise KernelError("paged_attention_ex: one 32-bit slope per head")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads):
+        raise KernelError("paged_attention_ex: one 32-bit sink per head")
     call("fx_paged_attention_ex", _ptr(q), int(ldq), int(ldqh), _ptr(k_pages), _ptr(v_pages), int(ldk), int(ldv), code(q),
          _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot), _ptr(out),
          int(ldo), int(ldoh), T, n_heads, n_kv_heads, key_dim, value_dim, int(window or 0), float(scale),
-         float(softcap or 0.0), _ptr(slopes), int(keep_first or 0), stream if stream is not None else stream_ptr())
+         float(softcap or 0.0), _ptr(slopes), int(keep_first or 0), _ptr(sinks), int(value_share),
+         stream if stream is not None else stream_ptr())
     return out
 
 
@@ -669,7 +766,8 @@ def general_attention_items(entries, n_heads: int, n_kv_heads: int):
 
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, page_size, positions, token_seq, seq_slot,
                       items, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim, window, scale, slopes=None,
-                      stream=None, n_splits=1, part_o=None, part_ml=None, kv_strides=None, keep_first=0):
+                      stream=None, n_splits=1, part_o=None, part_ml=None, kv_strides=None, keep_first=0, softcap=None,
+                      sinks=None, value_share=1):
     """:func:`paged_attention_ex` in bfloat16 on the tensor cores (see :func:`general_attention_ok`).  ``items``: the
     device copy of :func:`general_attention_items`, or None when every entry brings one token (a tile a token and
     kv head; nothing comes from the host, so a captured step replays unchanged).  ``n_splits`` > 1 (without items):
@@ -677,7 +775,9 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, pag
     value_dim] and ``part_ml`` float32 [T, heads, n_splits, 2] are scratch, and a second kernel adds the runs up.
     ``kv_strides`` = (k page stride, k head stride, v page stride, v head stride) in elements, for keys and values that
     do not lie [page][kv head][position][ld] (rows that hold all heads side by side); ``ldk`` / ``ldv`` stay the
-    distance between two positions."""
+    distance between two positions.  ``softcap``, ``sinks``, ``value_share``: as :func:`paged_attention_ex`."""
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads):
+        raise KernelError("general_attention: one 32-bit sink per head")
     strides = (ctypes.c_long * 4)(*[int(x) for x in kv_strides]) if kv_strides is not None else None
     global _launches
     n = items.shape[0] if items is not None else positions.numel()
@@ -687,7 +787,7 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, block_table, pag
          ctypes.cast(strides, c_void_p) if strides is not None else None, _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(token_seq), _ptr(seq_slot),
          _ptr(items), n, _ptr(out), int(ldo), int(ldoh), n_heads, n_kv_heads, key_dim, value_dim, int(window or 0),
          float(scale), _ptr(slopes), int(n_splits), _ptr(part_o), _ptr(part_ml), int(keep_first or 0),
-         stream if stream is not None else stream_ptr())
+         float(softcap or 0.0), _ptr(sinks), int(value_share), stream if stream is not None else stream_ptr())
     return out
 
 
@@ -710,17 +810,18 @@ def qk_norm_store(qkv, positions, token_seq, seq_slot, q_weight, k_weight, eps, 
 
 
 def latent_prep(q, dkv, positions, token_seq, seq_slot, c_weight, eps, cos_sin, rot_dims, q_plain, q_full, pages,
-                block_table, page_size, n_heads, plain_dim, rot_dim, rank, write_cache=True, status=None, stream=None):
+                block_table, page_size, n_heads, plain_dim, rot_dim, rank, write_cache=True, status=None, stream=None,
+                pairing=PAIR_ADJACENT):
     """The step between a latent attention's projections and its attention kernel: ``dkv`` rows [rank | rot_dim] become
-    the cached row (the latent normed with ``c_weight``, the key part rotated on neighbouring pairs by ``cos_sin``
-    [T, rot_dims / 2, 2]); ``q`` rows of heads [plain_dim | rot_dim] are split into ``q_plain`` [heads, T, plain_dim]
+    the cached row (the latent normed with ``c_weight``, the key part rotated by ``cos_sin`` [T, rot_dims / 2, 2] on
+    neighbouring pairs or, ``pairing`` PAIR_HALVES, on pairs (i, i + rot_dims / 2)); ``q`` rows of heads [plain_dim | rot_dim] are split into ``q_plain`` [heads, T, plain_dim]
     and the rotated part in columns rank.. of ``q_full`` [heads, T, rank + rot_dim].  ``q_plain`` None (and ``q_full``
     None): the queries stay token rows and their rotated parts are turned where they lie."""
     T = q.shape[0]
     call("fx_latent_prep", _ptr(q), _rows(q), _ptr(dkv), _rows(dkv), code(q), _ptr(positions), _ptr(token_seq),
          _ptr(seq_slot), _ptr(c_weight), code(c_weight), float(eps), _ptr(cos_sin), int(rot_dims), _ptr(q_plain),
          _ptr(q_full), _ptr(pages), _ptr(block_table), block_table.shape[1], page_size, T, n_heads, plain_dim, rot_dim,
-         rank, int(write_cache), _ptr(status), stream if stream is not None else stream_ptr())
+         rank, int(write_cache), _ptr(status), int(pairing), stream if stream is not None else stream_ptr())
 
 
 def rmsnorm_rows(x, weight, eps, out, stream=None):
@@ -731,25 +832,26 @@ def rmsnorm_rows(x, weight, eps, out, stream=None):
     return out
 
 
-def heads_to_tokens(x, out, gate=None, stream=None):
+def heads_to_tokens(x, out, gate=None, stream=None, gate_per_head=False):
     """out[t, h * V + v] = x[h, t, v] (* sigmoid(gate[t, h * V + v])): rows laid out head by head back into token
-    rows.  ``x`` contiguous [heads, T, V]; ``gate`` a row view of out's width."""
+    rows.  ``x`` contiguous [heads, T, V]; ``gate`` a row view of out's width, or with ``gate_per_head`` of one
+    number a head (sigmoid(gate[t, h]))."""
     H, T, V = x.shape
     if not x.is_contiguous() or (gate is not None and gate.dtype != x.dtype) or out.dtype != x.dtype:
         raise KernelError("heads_to_tokens: contiguous [heads, tokens, width] and one element type")
     call("fx_heads_to_tokens", _ptr(x), V, T * V, _ptr(gate), _rows(gate) if gate is not None else 0, _ptr(out), _rows(out),
-         code(x), T, H, V, stream if stream is not None else stream_ptr())
+         code(x), T, H, V, int(gate_per_head), stream if stream is not None else stream_ptr())
     return out
 
 
-def gate_heads_(x, gate, n_heads, stream=None):
+def gate_heads_(x, gate, n_heads, stream=None, gate_per_head=False):
     """x[t, c] *= sigmoid(gate[t, c]) over token rows of ``n_heads`` heads, in place (the same kernel as
     :func:`heads_to_tokens`, reading the rows where they lie)."""
     T, W = x.shape
     if gate.dtype != x.dtype or W % n_heads:
         raise KernelError("gate_heads_: one element type, a width that the heads divide")
     call("fx_heads_to_tokens", _ptr(x), _rows(x), W // n_heads, _ptr(gate), _rows(gate), _ptr(x), _rows(x), code(x), T,
-         n_heads, W // n_heads, stream if stream is not None else stream_ptr())
+         n_heads, W // n_heads, int(gate_per_head), stream if stream is not None else stream_ptr())
     return x
 
 
@@ -880,11 +982,12 @@ def prefill_attention_tc(q, k_pages, v_pages, block_table, page_size, items, seq
     return out
 
 
-def router_topk(logits, top_k, renorm, ids, weights, n_experts=None, stream=None):
-    """``n_experts``: the first columns of ``logits`` that are router logits (default: all)."""
+def router_topk(logits, top_k, renorm, ids, weights, n_experts=None, stream=None, extra=None):
+    """``n_experts``: the first columns of ``logits`` that are router logits (default: all).  ``extra``: see
+    :func:`route_small`."""
     T, E = logits.shape[0], (n_experts or logits.shape[1])
     call("fx_router_topk", _ptr(logits), _rows(logits), T, E, top_k, int(renorm), _ptr(ids), _ptr(weights),
-         stream if stream is not None else stream_ptr())
+         *_route_extra(extra), stream if stream is not None else stream_ptr())
 
 
 def moe_align(ids, n_experts, scratch, offsets, src_token, inv_perm, active=None, stream=None):

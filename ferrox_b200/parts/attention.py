@@ -16,7 +16,7 @@ import math
 import numpy as np
 import torch
 
-from ..cache.specs import CacheSpec, KvCacheSpec, PagedSpec, PagedTensorSpec
+from ..cache.specs import CacheSpec, KvCacheSpec, PagedSpec, PagedTensorSpec, StateSpec
 from ..kernels import ops
 from ..weights.loader import TensorDecl
 from .base import Mixer, build_part, register_part
@@ -287,9 +287,11 @@ class GqaAttention(Mixer):
 
 
 def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, batch, cache, n_heads, n_kv_heads,
-                      key_dim, value_dim, window, scale, slopes, rt, keep_first=0):
+                      key_dim, value_dim, window, scale, slopes, rt, keep_first=0, softcap=None, sinks=None,
+                      value_share=1):
     """Attention over pages in its general form (keys and values of different widths, strided queries and outputs, an
-    optional distance bias, a window that may keep the request's first positions visible), by the kernel that fits
+    optional distance bias, a window that may keep the request's first positions visible, capped scores, a learned
+    number per head in the softmax's denominator, key heads that share value heads), by the kernel that fits
     the step: tiles of (token, head) pairs on the tensor cores
     in bfloat16, a warp per (token, head) on the CUDA cores in 32-bit and for widths that are no multiple of 16."""
     per_sm = ops.general_attention_ok(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, key_dim, value_dim)
@@ -317,10 +319,134 @@ def general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, out, ldo, ldoh, 
         return ops.general_attention(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size,
                                      batch.positions, batch.token_seq, batch.seq_slot, items, out, ldo, ldoh, n_heads,
                                      n_kv_heads, key_dim, value_dim, window, scale, slopes=slopes, stream=batch.stream,
-                                     n_splits=n_splits, part_o=part_o, part_ml=part_ml, keep_first=keep_first)
+                                     n_splits=n_splits, part_o=part_o, part_ml=part_ml, keep_first=keep_first,
+                                     softcap=softcap, sinks=sinks, value_share=value_share)
     ops.paged_attention_ex(q, ldq, ldqh, k_pages, v_pages, ldk, ldv, cache.block_table, cache.page_size, batch.positions,
                            batch.token_seq, batch.seq_slot, out, ldo, ldoh, n_heads, n_kv_heads, key_dim, value_dim,
-                           window, scale, slopes=slopes, stream=batch.stream, keep_first=keep_first)
+                           window, scale, slopes=slopes, stream=batch.stream, keep_first=keep_first, softcap=softcap,
+                           sinks=sinks, value_share=value_share)
+
+
+class DifferentialAttention(Mixer):
+    """Two attention maps a head over the same values, the second taken off the first:
+
+        q = Wq x (H heads of [map 1 | map 2]),  k = Wk x (G kv heads likewise),  v = Wv x (G heads)
+        a short causal convolution on every channel of q, k and v; the maps' first rotary_dim elements rotated
+        a_j = softmax(cap(scale q_j . k_j)) v                                   (j = 1, 2; causal)
+        o   = rms(a_1 - lambda a_2) (1 - diff),   lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff
+        y   = Wo . concat(heads)
+
+    The attention kernels see 2H query heads on 2G key heads whose pairs read one value head (``value_share``).
+    So that a key head's query heads lie side by side, the rows of Wq (and of its convolution) are reordered when
+    they are loaded: kv head by kv head, map by map, then the heads of the group.  One kernel does the convolution,
+    the rotation and the cache write (``ops.conv_rotary_store``), one the combination of the maps with its norm
+    (``ops.diff_combine``).  The convolution's last inputs are a 32-bit state of the request."""
+
+    TAIL = "conv_tail"
+
+    @property
+    def graph_safe(self):
+        return self.position is None or self.position.graph_safe
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if s.n_heads % s.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if s.head_dim > ops.ATTENTION_MAX_KEY_DIM or s.value_dim > ops.ATTENTION_MAX_VALUE_DIM:
+            raise ValueError(f"head_dim={s.head_dim}, value_dim={s.value_dim}: at most {ops.ATTENTION_MAX_KEY_DIM} "
+                             f"and {ops.ATTENTION_MAX_VALUE_DIM}")
+        self.taps = int(s.conv_taps or 1)
+        if not 1 <= self.taps <= 16:
+            raise ValueError(f"conv_taps={s.conv_taps}: between 1 and 16")
+        self.position = build_part(s.position) if s.position is not None else None
+        if self.position is not None and not hasattr(self.position, "table"):
+            raise ValueError("differential attention rotates by a table of cos and sin: a rotary position part or none")
+        self.group = s.n_heads // s.n_kv_heads
+        self.nq, self.nk = 2 * s.n_heads, 2 * s.n_kv_heads
+        self.q_size, self.k_size = self.nq * s.head_dim, self.nk * s.head_dim
+        self.v_size, self.o_size = s.n_kv_heads * s.value_dim, s.n_heads * s.value_dim
+        self.channels = self.q_size + self.k_size + self.v_size
+        if s.softcap is not None and s.softcap <= 0:
+            raise ValueError(f"softcap={s.softcap}: the cap of the scores is positive")
+
+    def cache_spec(self):
+        s = self.spec
+        paged = PagedSpec((PagedTensorSpec("k", (self.nk, s.head_dim), lead_dims=1),
+                           PagedTensorSpec("v", (s.n_kv_heads, s.value_dim), lead_dims=1)), None)
+        state = StateSpec(parts=((self.TAIL, (self.taps - 1, self.channels)),)) if self.taps > 1 else None
+        return CacheSpec(paged=paged, state=state)
+
+    def tensor_decls(self):
+        s, p = self.spec, self.spec.prefix
+        d = [TensorDecl(p + "q", (self.q_size, s.hidden)), TensorDecl(p + "k", (self.k_size, s.hidden)),
+             TensorDecl(p + "v", (self.v_size, s.hidden))]
+        if s.conv_taps:
+            d += [TensorDecl(p + "q.conv", (self.q_size, self.taps)), TensorDecl(p + "k.conv", (self.k_size, self.taps)),
+                  TensorDecl(p + "v.conv", (self.v_size, self.taps))]
+        d += [TensorDecl(p + n, (s.head_dim,)) for n in ("lq1", "lk1", "lq2", "lk2")]
+        d.append(TensorDecl(p + "o", (s.hidden, self.o_size)))
+        return d
+
+    def _query_row_order(self):
+        """Row r of the reordered Wq is row order[r] of the stored one: (kv head, map, head of the group, element)
+        from (head, map, element)."""
+        s = self.spec
+        g, j, hg, e = torch.meshgrid(torch.arange(s.n_kv_heads), torch.arange(2), torch.arange(self.group),
+                                     torch.arange(s.head_dim), indexing="ij")
+        return (((g * self.group + hg) * 2 + j) * s.head_dim + e).reshape(-1)
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        s, p = self.spec, self.spec.prefix
+        order = self._query_row_order().to(rt.device)
+        ws = [src.get(p + "q")[order], src.get(p + "k"), src.get(p + "v")]
+        dt = _common_dtype(ws)
+        self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
+        if s.conv_taps:
+            cs = [src.get(p + "q.conv")[order], src.get(p + "k.conv"), src.get(p + "v.conv")]
+            self.conv_w = torch.cat([c.to(torch.float32) for c in cs], dim=0).contiguous()
+        else:
+            self.conv_w = torch.ones(self.channels, 1, dtype=torch.float32, device=rt.device)
+        lam = [src.get(p + n).to(torch.float32).cpu() for n in ("lq1", "lk1", "lq2", "lk2")]
+        # one number for the layer, worked out once in 32 bits
+        self.lam = float(torch.exp((lam[0] * lam[1]).sum()) - torch.exp((lam[2] * lam[3]).sum()) + torch.tensor(float(s.diff)))
+        self.w_o = src.get(p + "o")
+        if self.position is not None:
+            self.position.load(src, rt)
+
+    def reset_after_fault(self):
+        if self.position is not None:
+            self.position.reset_after_fault()
+
+    def forward_add(self, x, h, batch, cache):
+        self.forward_into(x, h, batch, cache, accumulate=True)
+
+    def forward_into(self, x, out, batch, cache, accumulate=False):
+        s, rt, st = self.spec, self.rt, batch.stream
+        T, D, V = x.shape[0], s.head_dim, s.value_dim
+        proj = rt.empty(T, self.channels)
+        ops.linear(x, self.w_qkv, proj, status=batch.status, stream=st, after_short_kernel=True)
+        tail = cache.states[self.TAIL] if self.taps > 1 else None
+        single = batch.max_new == 1      # a decode step: the kernel that reads the tail also moves it on
+        cos_sin = self.position.table(batch) if self.position is not None else None
+        rot = self.position.rotary_dim if self.position is not None else 0
+        pairing = self.position.pairing if self.position is not None else ops.PAIR_HALVES
+        q = rt.empty(T, self.q_size)
+        ops.conv_rotary_store(proj, self.conv_w, self.taps, tail, batch.positions, batch.token_seq, batch.seq_slot, cos_sin,
+                              rot, pairing, q, cache.k, cache.v, cache.block_table, cache.page_size, self.nq, self.nk, D,
+                              s.n_kv_heads, V, write_cache=cache.writes, update_tail=single and self.taps > 1,
+                              status=batch.status, stream=st)
+        if self.taps > 1 and not single:
+            ops.conv_tail_update(proj, self.channels, self.taps, tail, batch.token_seq, batch.seq_slot, batch.n_seqs,
+                                 stream=st)
+        maps = rt.empty(T, self.nq * V)
+        general_attention(q, q.stride(0), D, cache.k, cache.v, D, V, maps, maps.stride(0), V, batch, cache, self.nq,
+                          self.nk, D, V, None, s.scale, None, rt, softcap=s.softcap, value_share=2)
+        attn = rt.empty(T, self.o_size)
+        ops.diff_combine(maps, attn, s.n_heads, self.group, V, self.lam, s.norm_eps, 1.0 - float(s.diff), stream=st)
+        ops.linear(attn, self.w_o, out, accumulate=accumulate, status=batch.status, stream=st, after_short_kernel=True)
 
 
 register_part("gqa_attention", GqaAttention, replace=True)
+register_part("differential_attention", DifferentialAttention, replace=True)

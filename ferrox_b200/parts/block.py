@@ -73,7 +73,11 @@ class ParallelBlock(Block):
 
         x = norm1(h);  h += mixer(x);  h += ffn(x)
 
-    (``ffn`` None: the layer ends after the mixer.)  The sum h + (mixer + ffn) is made in 32 bits in the stream."""
+    (``ffn`` None: the layer ends after the mixer.)  The sum h + (mixer + ffn) is made in 32 bits in the stream.
+
+    ``residual_mult`` m other than 1:  h += m (mixer(x) + ffn(x)).  Both sublayers then add into a 32-bit buffer of
+    the stream's shape, and one kernel multiplies it, adds it to the stream and, where the next block starts with an
+    RMS norm, applies that to the new rows as well."""
 
     passes_norm = True
 
@@ -82,6 +86,7 @@ class ParallelBlock(Block):
         self.norm1 = build_part(spec.norm1)
         self.mixer = build_part(spec.mixer)
         self.ffn = build_part(spec.ffn) if spec.ffn is not None else None
+        self.mult = float(getattr(spec, "residual_mult", 1.0))
 
     def _parts(self):
         return [p for p in (self.norm1, self.mixer, self.ffn) if p is not None]
@@ -106,6 +111,8 @@ class ParallelBlock(Block):
         if x is None:
             with ops.trace_scope("norm"):
                 x = self.norm1.forward(h)
+        if self.mult != 1.0:
+            return self._forward_scaled(h, x, batch, cache, then_norm)
         with ops.trace_scope("mixer"):
             self.mixer.forward_add(x, h, batch, cache)
         if self.ffn is None:
@@ -114,6 +121,21 @@ class ParallelBlock(Block):
             if then_norm is not None and self.ffn.fuses_norm:
                 return self.ffn.forward_add(x, h, batch, then_norm=then_norm)
             self.ffn.forward_add(x, h, batch)
+        return None
+
+    def _forward_scaled(self, h, x, batch, cache, then_norm):
+        y = self.rt.empty(h.shape[0], h.shape[1], dtype=torch.float32)
+        with ops.trace_scope("mixer"):
+            self.mixer.forward_into(x, y, batch, cache, accumulate=False)
+        if self.ffn is not None:
+            with ops.trace_scope("feed-forward"):
+                self.ffn.forward_add(x, y, batch)
+        with ops.trace_scope("norm"):
+            rms = then_norm.as_rms() if then_norm is not None else None
+            if rms is not None:
+                out = self.rt.empty(h.shape[0], h.shape[1])
+                return ops.scaled_add_norm(h, y, self.mult, norm=(rms[0], rms[1], out), stream=batch.stream)
+            ops.scaled_add_norm(h, y, self.mult, stream=batch.stream)
         return None
 
 

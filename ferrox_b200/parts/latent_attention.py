@@ -20,7 +20,11 @@ of the latent-space form's when the latent is much wider than a head, at the pri
 rows.  ``expanded_gain`` estimates both; decoding always reads the latent rows (nothing is expanded for one token).
 
 Rotation: neighbouring pairs (2i, 2i + 1) of the first ``rotary_dims`` elements of the rot_dim part, pair i at
-base^(-2i / rotary_dims); angles, norms and scores are 32-bit.
+base^(-2i / rotary_dims); angles, norms and scores are 32-bit.  ``rotary_pairing="halves"`` pairs element i with
+element i + rotary_dims / 2 instead, and ``rotary_scaling`` stretches the frequencies (``ScaledRotarySpec``).
+
+``sink``: a learned number per head whose exponential joins the softmax's denominator (no key, no value, counted
+once).  ``gate_per_head``: the output gate is one number a head, sigmoid(g_h . x).
 """
 from __future__ import annotations
 
@@ -32,7 +36,7 @@ from ..kernels import ops
 from ..weights.loader import TensorDecl
 from .attention import _common_dtype, general_attention
 from .base import Mixer, build_part, register_part
-from .specs import AdjacentRotarySpec
+from .specs import AdjacentRotarySpec, ScaledRotarySpec
 
 
 # The expanded form of a prompt step is taken when its estimated cost is below this share of the latent-space form's
@@ -59,7 +63,22 @@ class LatentAttention(Mixer):
         self.q_width = s.n_heads * (s.head_dim + s.rot_dim)
         self.row = s.kv_rank + s.rot_dim
         self.o_size = s.n_heads * s.value_dim
-        self.rotary = build_part(AdjacentRotarySpec(rotary_dim=max(2, s.rotary_dims), theta=s.rotary_base))
+        pairing = getattr(s, "rotary_pairing", "adjacent")
+        scaling = getattr(s, "rotary_scaling", None)
+        if pairing not in ("adjacent", "halves"):
+            raise ValueError(f"rotary_pairing={pairing!r}: adjacent or halves")
+        if pairing == "adjacent":
+            if scaling is not None:
+                raise ValueError("latent attention: stretched frequencies come with the halves pairing")
+            self.rotary = build_part(AdjacentRotarySpec(rotary_dim=max(2, s.rotary_dims), theta=s.rotary_base))
+        else:
+            f, o, fa, sl = scaling if scaling is not None else (None, 0.0, 0.0, 0.0)
+            self.rotary = build_part(ScaledRotarySpec(rotary_dim=max(2, s.rotary_dims), theta=s.rotary_base, factor=f,
+                                                      original=o, fast=fa, slow=sl))
+        self.pairing = ops.PAIR_ADJACENT if pairing == "adjacent" else ops.PAIR_HALVES
+        self.gate_per_head = bool(getattr(s, "gate_per_head", False)) and s.output_gate
+        self.gate_rows = (s.n_heads if self.gate_per_head else self.o_size) if s.output_gate else 0
+        self.sink_name = getattr(s, "sink", None)
         self._groups = {}
 
     def cache_spec(self):
@@ -77,7 +96,9 @@ class LatentAttention(Mixer):
               TensorDecl(p + "uk", (s.n_heads * s.head_dim, s.kv_rank)),
               TensorDecl(p + "uv", (s.n_heads * s.value_dim, s.kv_rank))]
         if s.output_gate:
-            d.append(TensorDecl(p + "g", (self.o_size, s.hidden)))
+            d.append(TensorDecl(p + "g", (self.gate_rows, s.hidden)))
+        if self.sink_name:
+            d.append(TensorDecl(p + self.sink_name, (s.n_heads,)))
         d.append(TensorDecl(p + "o", (s.hidden, self.o_size)))
         return d
 
@@ -90,7 +111,12 @@ class LatentAttention(Mixer):
         if s.output_gate:
             first.append(src.get(p + "g"))
         dt = _common_dtype(first)
+        rows = sum(w.shape[0] for w in first)
+        if rows % 8:
+            # (a gate of one row a head: rows of zeros behind it keep the product's rows 16 bytes apart in 16 bits)
+            first.append(torch.zeros(8 - rows % 8, s.hidden, dtype=dt, device=first[0].device))
         self.w_in = torch.cat([w.to(dt) for w in first], dim=0).contiguous()
+        self.sink = src.get(p + self.sink_name).to(torch.float32).contiguous() if self.sink_name else None
         self.w_uq = src.get(p + "uq") if s.q_rank else None
         self.q_norm = src.get(p + "dq.norm") if s.q_rank else None
         self.c_norm = src.get(p + "dkv.norm")
@@ -194,13 +220,13 @@ class LatentAttention(Mixer):
             q = proj[:, :self.q_width]
             rest = self.q_width
         dkv = proj[:, rest:rest + row]
-        gate = proj[:, rest + row:] if s.output_gate else None
+        gate = proj[:, rest + row:rest + row + self.gate_rows] if s.output_gate else None
         pages = cache.pages["kv"]
         cos_sin = self.rotary.table(batch) if s.rotary_dims > 0 else None
         # cache write; the queries' rotated parts turned where they lie
         ops.latent_prep(q, dkv, batch.positions, batch.token_seq, batch.seq_slot, self.c_norm, s.norm_eps, cos_sin,
                         s.rotary_dims, None, None, pages, cache.block_table, ps, H, D, R, C, write_cache=True,
-                        status=batch.status, stream=st)
+                        status=batch.status, stream=st, pairing=self.pairing)
         src_pages, table, rows_of, items, n_copies = self._expanded_plan(batch, cache)
         seen = rt.empty(n_copies, ps * row)
         ops.gather_rows(pages.view(pages.shape[0], ps * row), src_pages, seen, stream=st)
@@ -211,9 +237,9 @@ class LatentAttention(Mixer):
         k_view, v_view = kv, kv[:, H * (D + R):]
         ops.general_attention(q, q.stride(0), D + R, k_view, v_view, wide, wide, table, ps, batch.positions, batch.token_seq,
                               rows_of, items, attn, attn.stride(0), V, H, H, D + R, V, s.window, s.scale, stream=st,
-                              kv_strides=(ps * wide, D + R, ps * wide, V))
+                              kv_strides=(ps * wide, D + R, ps * wide, V), sinks=self.sink)
         if gate is not None:
-            ops.gate_heads_(attn, gate, H, stream=st)
+            ops.gate_heads_(attn, gate, H, stream=st, gate_per_head=self.gate_per_head)
         ops.linear(attn, self.w_o, out, accumulate=accumulate, status=batch.status, stream=st, after_short_kernel=True)
 
     def forward_into(self, x, out, batch, cache, accumulate=False):
@@ -234,25 +260,25 @@ class LatentAttention(Mixer):
             q = proj[:, :self.q_width]
             rest = self.q_width
         dkv = proj[:, rest:rest + row]
-        gate = proj[:, rest + row:] if s.output_gate else None
+        gate = proj[:, rest + row:rest + row + self.gate_rows] if s.output_gate else None
         pages = cache.pages["kv"]
         q_plain = rt.empty(H, T, D)
         q_full = rt.empty(H, T, row)
         cos_sin = self.rotary.table(batch) if s.rotary_dims > 0 else None
         ops.latent_prep(q, dkv, batch.positions, batch.token_seq, batch.seq_slot, self.c_norm, s.norm_eps, cos_sin,
                         s.rotary_dims, q_plain, q_full, pages, cache.block_table, cache.page_size, H, D, R, C,
-                        write_cache=cache.writes, status=batch.status, stream=st)
+                        write_cache=cache.writes, status=batch.status, stream=st, pairing=self.pairing)
         offsets, heads = self._head_groups(T)
         ops.grouped_linear(q_plain.view(H * T, D), self.w_uk_t, q_full.view(H * T, row)[:, :C], offsets, heads, T,
                            status=batch.status, stream=st)
         o_lat = rt.empty(H, T, C)
         general_attention(q_full, row, T * row, pages, pages, row, row, o_lat, C, T * C, batch, cache, H, 1, row, C,
-                          s.window, s.scale, None, rt)
+                          s.window, s.scale, None, rt, sinks=self.sink)
         o_heads = rt.empty(H, T, V)
         ops.grouped_linear(o_lat.view(H * T, C), self.w_uv, o_heads.view(H * T, V), offsets, heads, T,
                            status=batch.status, stream=st)
         attn = rt.empty(T, self.o_size)
-        ops.heads_to_tokens(o_heads, attn, gate=gate, stream=st)
+        ops.heads_to_tokens(o_heads, attn, gate=gate, stream=st, gate_per_head=self.gate_per_head)
         ops.linear(attn, self.w_o, out, accumulate=accumulate, status=batch.status, stream=st, after_short_kernel=True)
 
 

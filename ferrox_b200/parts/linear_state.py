@@ -18,6 +18,14 @@ heads' read-outs are RMS-normed together, weighted, and gated by sigmoid(Wg x).
 (both terms read the state of the token before), w = exp(-rate sigmoid(W2 tanh(W1 x) + w0)), a = sigmoid(Wa x + ba);
 each head's o is RMS-normed, the concatenated heads weighted and gated by sigmoid(Wg x).
 
+``mlstm``:  per head a state S [head_dim, value_dim], a normaliser n [head_dim] and the running maximum m of the
+gates' logarithms (m starts at 0),
+
+    i = cap tanh((Wi x + bi) / cap);   f = logsigmoid(cap tanh((Wf x + bf) / cap));   m' = max(f + m, i)
+    S <- exp(f + m - m') S + exp(i - m') k v^T;   n likewise with k alone;   o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+
+with q = Wq x head_dim^(-1/2); each head's o is RMS-normed, the concatenated heads weighted and gated by sigmoid(Wg x).
+
 The states live in the cache manager's slots as 32-bit tensors; the recurrences, the gates and the norms are
 32-bit (``csrc/linear_state.cu``); the projections run in the engine's dtype.  Tokens of a request are taken in
 order whatever the step looks like, so a position's output does not depend on how the request was cut.
@@ -216,6 +224,76 @@ class GeneralDeltaRule(_StateMixer):
         ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
 
 
+class Mlstm(_StateMixer):
+    """One product for everything the mixer reads from its input, rows [q | k | v | gate | i | f], written in 32 bits
+    (all but the gate enters the recurrence); ``ops.mlstm_scan`` (gates, running maximum, state, read-out);
+    ``ops.gated_group_norm`` (per-head RMS, weight, sigmoid gate); output product."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if not s.gate_cap > 0:
+            raise ValueError(f"gate_cap={s.gate_cap}: the cap of the gates is positive")
+        self.qk = s.n_heads * s.head_dim
+        self.vv = s.n_heads * s.value_dim
+        self.copies = None      # copies of the normaliser and the maximum the state keeps (asked of the kernels once)
+
+    def _copies(self):
+        if self.copies is None:
+            self.copies = ops.mlstm_column_blocks(self.spec.head_dim, self.spec.value_dim)
+        return self.copies
+
+    def cache_spec(self):
+        s, z = self.spec, self._copies()
+        return CacheSpec(state=StateSpec(parts=(
+            ("matrix", (s.n_heads, s.value_dim, s.head_dim)),       # S, column by column
+            ("normalizer", (s.n_heads, z, s.head_dim)),             # n, one copy for each block of columns
+            ("log_max", (s.n_heads, z)),                            # m, likewise
+        )))
+
+    def tensor_decls(self):
+        s, p = self.spec, self.spec.prefix
+        return [
+            TensorDecl(p + "q", (self.qk, s.hidden)), TensorDecl(p + "k", (self.qk, s.hidden)),
+            TensorDecl(p + "v", (self.vv, s.hidden)), TensorDecl(p + "g", (self.vv, s.hidden)),
+            TensorDecl(p + "o", (s.hidden, self.vv)), TensorDecl(p + "norm", (self.vv,), init="ones"),
+            TensorDecl(p + "i", (s.n_heads, s.hidden)), TensorDecl(p + "i.b", (s.n_heads,)),
+            TensorDecl(p + "f", (s.n_heads, s.hidden)), TensorDecl(p + "f.b", (s.n_heads,)),
+        ]
+
+    def load(self, src, rt):
+        super().load(src, rt)
+        s, p = self.spec, self.spec.prefix
+        ws = [src.get(p + n) for n in ("q", "k", "v", "g", "i", "f")]
+        rows = sum(w.shape[0] for w in ws)
+        if rows % 8:     # (rows of zeros keep the product's output rows a multiple of 32 bytes wide)
+            ws.append(torch.zeros(8 - rows % 8, s.hidden, dtype=ws[0].dtype, device=ws[0].device))
+        self.w_in = _cat_rows(ws)
+        self.i_bias = src.get(p + "i.b").to(torch.float32).contiguous()
+        self.f_bias = src.get(p + "f.b").to(torch.float32).contiguous()
+        self.norm_w = src.get(p + "norm")
+        self.w_o = src.get(p + "o")
+
+    def forward_into(self, x, out, batch, cache, accumulate=False):
+        s, rt = self.spec, self.rt
+        T, H, D, V = x.shape[0], s.n_heads, s.head_dim, s.value_dim
+        f32 = torch.float32
+        proj = rt.empty(T, self.w_in.shape[0], dtype=f32)
+        ops.linear(x, self.w_in, proj, status=batch.status, stream=batch.stream)
+        q, k = proj[:, :self.qk], proj[:, self.qk:2 * self.qk]
+        v = proj[:, 2 * self.qk:2 * self.qk + self.vv]
+        gate = proj[:, 2 * self.qk + self.vv:2 * self.qk + 2 * self.vv]
+        gates = proj[:, 2 * self.qk + 2 * self.vv:]       # [i | f] as projected
+        read = rt.empty(T, self.vv, dtype=f32)
+        ops.mlstm_scan(q, k, v, gates, self.i_bias, self.f_bias, s.gate_cap, float(D) ** -0.5, cache.states["matrix"],
+                       cache.states["normalizer"], cache.states["log_max"], read, batch.token_seq, batch.seq_slot,
+                       batch.n_seqs, H, D, V, stream=batch.stream)
+        y = rt.empty(T, self.vv)
+        ops.gated_group_norm(read, gate, self.norm_w, s.norm_eps, "sigmoid", y, H, V, stream=batch.stream)
+        ops.linear(y, self.w_o, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
+
+
+register_part("mlstm", Mlstm, replace=True)
 register_part("gated_delta_rule", GatedDeltaRule, replace=True)
 register_part("general_delta_rule", GeneralDeltaRule, replace=True)
 register_part("decayed_linear_attention", DecayedLinearAttention, replace=True)

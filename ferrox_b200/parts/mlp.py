@@ -1,4 +1,4 @@
-"""Dense feed-forwards.  SwiGLU: down( silu(gate x) * (up x) ), no bias; plain: down( relu(up x)^2 )
+"""Dense feed-forwards.  SwiGLU: down( silu(gate x) * (up x) ), with or without biases; plain: down( relu(up x)^2 )
 (reference: crates/ferrox-moe/src/lib.rs:655-658; decoder.rs:2902-2913)."""
 from __future__ import annotations
 
@@ -16,7 +16,9 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 class SwigluMlp(FeedForward):
-    """down( act(gate x) * (up x) ); ``spec.activation`` names act (SiLU unless the spec says ReLU)."""
+    """down( act(gate x) * (up x) ); ``spec.activation`` names act (SiLU unless the spec says ReLU).  With
+    ``spec.bias_names`` every projection has a bias: down( act(gate x + bg) * (up x + bu) ) + bd; the first product
+    then writes [gate | up] with its bias and one kernel applies the gate."""
 
     graph_safe = True
 
@@ -26,19 +28,31 @@ class SwigluMlp(FeedForward):
         ops.gate_code(self.activation)   # an unknown activation fails here, by name
         names = getattr(spec, "tensor_names", None) or ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
         self._gate, self._up, self._down = (spec.prefix + n for n in names)
+        biases = getattr(spec, "bias_names", None)
+        self._biases = tuple(spec.prefix + n for n in biases) if biases else None
 
     def tensor_decls(self):
         s = self.spec
-        return [
+        d = [
             TensorDecl(self._gate, (s.intermediate, s.hidden)),
             TensorDecl(self._up, (s.intermediate, s.hidden)),
             TensorDecl(self._down, (s.hidden, s.intermediate)),
         ]
+        if self._biases:
+            d += [TensorDecl(self._biases[0], (s.intermediate,)), TensorDecl(self._biases[1], (s.intermediate,)),
+                  TensorDecl(self._biases[2], (s.hidden,))]
+        return d
 
     def load(self, src, rt):
         super().load(src, rt)
         self.w_gu = pack_gate_up(src.get(self._gate), src.get(self._up))
         self.w_down = src.get(self._down)
+        self.b_gu = self.b_down = None
+        if self._biases:
+            bg, bu = src.get(self._biases[0]), src.get(self._biases[1])
+            dt = torch.float32 if torch.float32 in (bg.dtype, bu.dtype) else bg.dtype
+            self.b_gu = torch.cat([bg.to(dt), bu.to(dt)]).contiguous()
+            self.b_down = src.get(self._biases[2])
 
     def forward_add(self, x, h, batch):
         self.forward_into(x, h, batch, accumulate=True)
@@ -46,9 +60,16 @@ class SwigluMlp(FeedForward):
     def forward_into(self, x, out, batch, accumulate=False):
         T, I = x.shape[0], self.spec.intermediate
         act = self.rt.empty(T, I)
-        # act(gate) * up in the epilogue
-        ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream, activation=self.activation)
-        ops.linear(act, self.w_down, out, accumulate=accumulate, status=batch.status, stream=batch.stream)
+        if self.b_gu is not None:
+            # biases: [gate | up] with its bias from the product's epilogue, then act(gate) * up
+            gu = self.rt.empty(T, 2 * I)
+            ops.linear(x, self.w_gu, gu, bias=self.b_gu, status=batch.status, stream=batch.stream)
+            ops.silu_mul(gu, act, stream=batch.stream, activation=self.activation)
+        else:
+            # act(gate) * up in the epilogue
+            ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream, activation=self.activation)
+        ops.linear(act, self.w_down, out, bias=self.b_down, accumulate=accumulate, status=batch.status,
+                   stream=batch.stream)
 
 
 class PlainMlp(FeedForward):

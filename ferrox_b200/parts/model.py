@@ -109,7 +109,8 @@ class DecoderModel(Part):
                 ops.embed_pos(self.embedding, batch.token_ids, self.position_table, batch.positions, h,
                               status=batch.status, stream=batch.stream)
             else:
-                ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream)
+                ops.embed(self.embedding, batch.token_ids, h, status=batch.status, stream=batch.stream,
+                          scale=float(getattr(s, "embedding_scale", 1.0)))
             if self.embedding_norm is not None:
                 self.embedding_norm.forward_in_place(h)
         x = None    # the next block's first norm of h, when the block before it has computed it

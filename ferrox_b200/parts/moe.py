@@ -9,7 +9,10 @@ Variants the spec can ask for: ``scores="sigmoid"`` (the weights are sigmoid(log
 choice is the same, both scores rise with the logit); ``weight_on_input`` (y = sum_k expert_e(w_k x): the rows are
 scaled while they are brought into expert order, and the combination adds the experts' outputs as they are);
 ``activation`` (what the gate passes through, e.g. the clamped unit with its limit; the shared expert may have its
-own constants).
+own constants); ``plain_activation`` (experts without a gate, down(act(up x)), the shared expert likewise: the
+products' epilogues apply act); ``choice_bias`` (a number per expert added to the sigmoid scores for the choice only;
+the weights use the scores without it), ``weight_scale`` (a factor on the final weights) and ``renorm_eps`` (added to
+the sum the kept scores are divided by).
 
 Reference: router crates/ferrox-moe/src/lib.rs:333-355, expert :619-659, combine
 :735-752, shared expert and its sigmoid gate crates/ferrox-models/src/decoder.rs:
@@ -61,8 +64,19 @@ class SoftmaxTopkMoe(FeedForward):
         self.weight_on_input = bool(getattr(s, "weight_on_input", False))
         self.activation = getattr(s, "activation", "silu")
         self.shared_activation = getattr(s, "shared_activation", None) or self.activation
-        self._gated = ops.gated_arg(self.activation)      # unknown activations fail here, by name
-        ops.gated_arg(self.shared_activation)
+        self.plain = getattr(s, "plain_activation", None)
+        if self.plain is not None:
+            ops.unary_code(self.plain)                    # unknown activations fail here, by name
+            if self.weight_on_input:
+                raise ValueError("experts without a gate take their routing weight on the output")
+            self._gated = False
+        else:
+            self._gated = ops.gated_arg(self.activation)
+            ops.gated_arg(self.shared_activation)
+        self._parts = ("up", "down") if self.plain else ("gate", "up", "down")
+        self.choice_bias_name = getattr(s, "choice_bias", None)
+        if self.choice_bias_name and self.scores != "sigmoid":
+            raise ValueError("a choice bias goes with sigmoid scores")
         self._route_mode = int(bool(s.norm_topk_prob)) | (2 if self.scores == "sigmoid" else 0)
         router, expert, shared = getattr(s, "tensor_names", None) or (
             "gate.weight", "experts.{e}.{part}_proj.weight", "shared_expert.{part}_proj.weight")
@@ -76,21 +90,19 @@ class SoftmaxTopkMoe(FeedForward):
     def tensor_decls(self):
         s, p = self.spec, self.spec.prefix
         d = [TensorDecl(self._router_name, (s.n_experts, s.hidden))]
+        shape = lambda part, inner: (s.hidden, inner) if part == "down" else (inner, s.hidden)
         for e in range(s.n_experts):
-            d += [
-                TensorDecl(self._expert_name(e, "gate"), (s.expert_intermediate, s.hidden)),
-                TensorDecl(self._expert_name(e, "up"), (s.expert_intermediate, s.hidden)),
-                TensorDecl(self._expert_name(e, "down"), (s.hidden, s.expert_intermediate)),
-            ]
+            d += [TensorDecl(self._expert_name(e, part), shape(part, s.expert_intermediate)) for part in self._parts]
+        if self.choice_bias_name:
+            d.append(TensorDecl(p + self.choice_bias_name, (s.n_experts,)))
         if s.shared_intermediate > 0:
-            d += [
-                TensorDecl(self._shared_name("gate"), (s.shared_intermediate, s.hidden)),
-                TensorDecl(self._shared_name("up"), (s.shared_intermediate, s.hidden)),
-                TensorDecl(self._shared_name("down"), (s.hidden, s.shared_intermediate)),
-            ]
+            d += [TensorDecl(self._shared_name(part), shape(part, s.shared_intermediate)) for part in self._parts]
             if s.shared_gate:
-                d.append(TensorDecl(p + "shared_expert_gate.weight", (1, s.hidden), optional=True))
+                d.append(TensorDecl(self._shared_gate_name(), (1, s.hidden), optional=True))
         return d
+
+    def _shared_gate_name(self):
+        return self.spec.prefix + (getattr(self.spec, "shared_gate_name", None) or "shared_expert_gate.weight")
 
     def load(self, src, rt):
         super().load(src, rt)
@@ -98,20 +110,32 @@ class SoftmaxTopkMoe(FeedForward):
         self.w_router = src.get(self._router_name)
         E, I, H = s.n_experts, s.expert_intermediate, s.hidden
         # If any expert tensor is stored in 32 bits, the packed buffers are 32-bit.
-        names = [self._expert_name(e, n) for e in range(E) for n in ("gate", "up", "down")]
+        names = [self._expert_name(e, n) for e in range(E) for n in self._parts]
         dt = torch.float32 if any(src.dtype_of(n) == torch.float32 for n in names) else rt.dtype
-        self.w_gu = torch.empty(E, 2 * I, H, dtype=dt, device=rt.device)
+        # (experts without a gate: w_gu holds the up rows alone)
+        self.w_gu = torch.empty(E, I if self.plain else 2 * I, H, dtype=dt, device=rt.device)
         self.w_down = torch.empty(E, H, I, dtype=dt, device=rt.device)
         for e in range(E):
-            self.w_gu[e, :I].copy_(src.get(self._expert_name(e, "gate")))
-            self.w_gu[e, I:].copy_(src.get(self._expert_name(e, "up")))
+            if self.plain:
+                self.w_gu[e].copy_(src.get(self._expert_name(e, "up")))
+            else:
+                self.w_gu[e, :I].copy_(src.get(self._expert_name(e, "gate")))
+                self.w_gu[e, I:].copy_(src.get(self._expert_name(e, "up")))
             self.w_down[e].copy_(src.get(self._expert_name(e, "down")))
         self.w_shared_gu = self.w_shared_down = self.w_shared_gate = None
         if s.shared_intermediate > 0:
-            self.w_shared_gu = pack_gate_up(src.get(self._shared_name("gate")), src.get(self._shared_name("up")))
+            if self.plain:
+                self.w_shared_gu = src.get(self._shared_name("up"))
+            else:
+                self.w_shared_gu = pack_gate_up(src.get(self._shared_name("gate")), src.get(self._shared_name("up")))
             self.w_shared_down = src.get(self._shared_name("down"))
-            if s.shared_gate and src.has(p + "shared_expert_gate.weight"):
-                self.w_shared_gate = src.get(p + "shared_expert_gate.weight").reshape(1, H).contiguous()
+            if s.shared_gate and src.has(self._shared_gate_name()):
+                self.w_shared_gate = src.get(self._shared_gate_name()).reshape(1, H).contiguous()
+        # what the routing kernels take beside the mode: the choice bias (32-bit), a factor on the weights, the
+        # number added to the sum the kept scores are divided by
+        bias = src.get(p + self.choice_bias_name).to(torch.float32).contiguous() if self.choice_bias_name else None
+        scale, eps = float(getattr(s, "weight_scale", 1.0)), float(getattr(s, "renorm_eps", 0.0))
+        self._route_extra = (bias, scale, eps) if (bias is not None or scale != 1.0 or eps != 0.0) else None
         # router rows and the shared expert's gate row share one product: [E (+1), H]
         self.w_route = self.w_router
         if self.w_shared_gate is not None:
@@ -127,7 +151,10 @@ class SoftmaxTopkMoe(FeedForward):
         s, rt = self.spec, self.rt
         T, Is = x.shape[0], s.shared_intermediate
         sact = rt.empty(T, Is)
-        ops.gated_linear(x, self.w_shared_gu, sact, status=batch.status, stream=st, activation=self.shared_activation)
+        if self.plain:
+            ops.linear(x, self.w_shared_gu, sact, status=batch.status, stream=st, activation=self.plain)
+        else:
+            ops.gated_linear(x, self.w_shared_gu, sact, status=batch.status, stream=st, activation=self.shared_activation)
         shared = rt.empty(T, s.hidden)
         ops.linear(sact, self.w_shared_down, shared, status=batch.status, stream=st)
         return shared
@@ -148,6 +175,7 @@ class SoftmaxTopkMoe(FeedForward):
         # kernel (three dependent launches otherwise, each a few microseconds of waiting for the one before).
         fused = ops.route_fused_ok(x, self.w_route, E, K)
         mode, gated, scaled = self._route_mode, self._gated, self.weight_on_input
+        unary, extra = self.plain, self._route_extra
         tc = ops.tc_ok(x, self.w_gu) and I % 8 == 0 and E <= ops.TC_MAX_GROUPS
         tiles = expert_tile_tokens(T, K, E) if tc and T >= SWAP_MIN_TOKENS and E <= ops.TC_SWAP_MAX_GROUPS else None
         small = tiles is None and T <= ops.SKINNY_MAX_TOKENS and ops.skinny_ok(x, self.w_gu) and I % 32 == 0
@@ -179,17 +207,17 @@ class SoftmaxTopkMoe(FeedForward):
             # was before it) fill every SM.
             xp = rt.empty(T * K, H) if tiles is not None or scaled else None
             ops.route_fused(x, self.w_route, logits, K, mode | (4 if scaled else 0), ids, weights, offsets, src_token, inv_perm, active,
-                            n_experts=E, xp_out=xp, stream=st)
+                            n_experts=E, xp_out=xp, stream=st, extra=extra)
             if overlap:
                 shared = self._shared_on_side(x, batch)
         elif T <= ops.ROUTE_SMALL_MAX_TOKENS and E <= ops.ROUTE_SMALL_MAX_EXPERTS:
             ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
             ops.route_small(logits, K, mode, ids, weights, offsets, src_token, inv_perm, active,
-                            n_experts=E, stream=st)
+                            n_experts=E, stream=st, extra=extra)
         else:
             ops.linear(x, self.w_route, logits, status=batch.status, stream=st)
             ops.route(logits, K, mode, ids, weights, self._scratch, offsets, src_token, inv_perm, active,
-                      n_experts=E, stream=st)
+                      n_experts=E, stream=st, extra=extra)
 
         act = rt.empty(T * K, I)
         y = rt.empty(T * K, H)
@@ -206,13 +234,13 @@ class SoftmaxTopkMoe(FeedForward):
                 ops.gather_rows(x, src_token, xp, stream=st)
             # (the offsets were written by the routing, before the gather: both products may fetch weights early;
             # when one kernel did both, the first product waits for it before it reads the offsets)
-            ops.gemm_tc_swap(xp, self.w_gu, act, gated=gated, group_offsets=offsets, tokens_per_tile=tiles[0],
+            ops.gemm_tc_swap(xp, self.w_gu, act, gated=gated, unary=unary, group_offsets=offsets, tokens_per_tile=tiles[0],
                              weights_first=not fused and not scaled, status=batch.status, stream=st)
             ops.gemm_tc_swap(act, self.w_down, y, group_offsets=offsets, tokens_per_tile=tiles[1],
                              weights_first=True, status=batch.status, stream=st)
         elif small:
             # very few tokens: every expert that was chosen is streamed once, gate/up fused with SiLU
-            ops.gemm_skinny(xp if scaled else x, self.w_gu, act, gated=gated, x_rows=None if scaled else src_token,
+            ops.gemm_skinny(xp if scaled else x, self.w_gu, act, gated=gated, unary=unary, x_rows=None if scaled else src_token,
                             group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)
             ops.gemm_skinny(act, self.w_down, y, group_offsets=offsets, active_groups=active, tokens_hint=T, stream=st)
         elif big:
@@ -220,13 +248,16 @@ class SoftmaxTopkMoe(FeedForward):
             if xp is None:
                 xp = rt.empty(T * K, H)
                 ops.gather_rows(x, src_token, xp, stream=st)
-            ops.gemm_tc(xp, self.w_gu, act, gated=gated, group_offsets=offsets, status=batch.status, stream=st)
+            ops.gemm_tc(xp, self.w_gu, act, gated=gated, unary=unary, group_offsets=offsets, status=batch.status, stream=st)
             ops.gemm_tc(act, self.w_down, y, group_offsets=offsets, status=batch.status, stream=st)
         else:
-            gu = rt.empty(T * K, 2 * I)
+            gu = act if unary else rt.empty(T * K, 2 * I)
             ops.gemm(xp if scaled else x, self.w_gu, gu, a_rows=None if scaled else src_token, group_offsets=offsets,
                      stream=st)
-            ops.silu_mul(gu, act, stream=st, activation=self.activation)
+            if unary:
+                ops.relu_square_(act, stream=st)
+            else:
+                ops.silu_mul(gu, act, stream=st, activation=self.activation)
             ops.gemm(act, self.w_down, y, group_offsets=offsets, stream=st)
 
         gate_logit = None

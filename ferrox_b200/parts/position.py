@@ -14,6 +14,8 @@ carries split-half and adjacent pairing and per-band frequency factors side by s
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..kernels import ops
@@ -38,6 +40,7 @@ class RotaryEncoding(PositionEncoding):
 
     graph_safe = True
     pairing = ops.PAIR_HALVES
+    magnitude = 1.0     # a factor on cos and sin
 
     def frequencies(self) -> torch.Tensor:
         """[rotary_dim / 2] float32 on the CPU: 1 / theta^(2i/r), the reference's expression in 32 bits."""
@@ -53,14 +56,14 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary_dim={self.rotary_dim}: pairs need an even width")
         self.inv_freq = self.frequencies().to(rt.device)
         # what makes two parts' tables of a step the same table
-        self._table_key = ("rotary table", self.rotary_dim, self.inv_freq.cpu().numpy().tobytes())
+        self._table_key = ("rotary table", self.rotary_dim, self.inv_freq.cpu().numpy().tobytes(), float(self.magnitude))
 
     def table(self, batch):
         """cos and sin of this step's angles, made once and shared by every layer with the same frequencies."""
         t = batch.shared.get(self._table_key)
         if t is None:
             t = self.rt.empty(batch.n_tokens, self.rotary_dim // 2, 2, dtype=torch.float32)
-            ops.rope_table(batch.positions, self.inv_freq, t, stream=batch.stream)
+            ops.rope_table(batch.positions, self.inv_freq, t, stream=batch.stream, magnitude=self.magnitude)
             batch.shared[self._table_key] = t
         return t
 
@@ -95,6 +98,41 @@ class RopeAdjacent(RotaryEncoding):
         return torch.pow(torch.tensor(float(self.spec.theta), dtype=torch.float64), -2.0 * i / float(r)).to(torch.float32)
 
 
+class RopeScaled(RotaryEncoding):
+    """Pairs (i, i + rotary_dim/2) at frequencies stretched for contexts beyond the original one (see
+    ``ScaledRotarySpec``): a ramp over the pair index blends f_i / factor (slow pairs, whose wavelength exceeds the
+    original context) with f_i (fast pairs), and cos and sin carry the factor 0.1 ln(factor) + 1.  Worked out in 64
+    bits and rounded once; the angle position * frequency and its cos and sin are 32-bit on the device."""
+
+    pairing = ops.PAIR_HALVES
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        s = spec
+        if s.factor is not None:
+            if not (s.factor > 0 and s.original > 0 and s.fast > 0 and s.slow > 0 and s.theta > 1):
+                raise ValueError("rope_scaled: factor, original, fast, slow are positive and theta exceeds 1")
+            self.magnitude = 0.1 * math.log(float(s.factor)) + 1.0
+
+    def frequencies(self):
+        s = self.spec
+        r, half = int(s.rotary_dim), int(s.rotary_dim) // 2
+        i = torch.arange(0, half, dtype=torch.float64)
+        f = torch.pow(torch.tensor(float(s.theta), dtype=torch.float64), -2.0 * i / float(r))
+        if s.factor is not None:
+            def pair_of(turns):
+                return r * math.log(float(s.original) / (2.0 * math.pi * turns)) / (2.0 * math.log(float(s.theta)))
+
+            lo = max(math.floor(pair_of(float(s.fast))), 0)
+            hi = min(math.ceil(pair_of(float(s.slow))), r - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / float(s.factor) * ramp + f * (1.0 - ramp)
+        return f.to(torch.float32)
+
+    def in_decode_kernel(self, batch, head_dim):
+        return None if self.magnitude != 1.0 else super().in_decode_kernel(batch, head_dim)
+
+
 class NoPosition(PositionEncoding):
     """No position encoding: keys and queries are stored as projected."""
 
@@ -114,3 +152,4 @@ class NoPosition(PositionEncoding):
 register_part("rope_neox", RopeNeox, replace=True)
 register_part("no_position", NoPosition, replace=True)
 register_part("rope_adjacent", RopeAdjacent, replace=True)
+register_part("rope_scaled", RopeScaled, replace=True)

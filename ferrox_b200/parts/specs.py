@@ -59,6 +59,23 @@ class AdjacentRotarySpec:
 
 
 @dataclass(frozen=True)
+class ScaledRotarySpec:
+    """Rotary position encoding on pairs (i, i + rotary_dim/2) whose frequencies are stretched for contexts longer
+    than the ``original`` one: with pair(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(
+    pair(fast)), 0), hi = min(ceil(pair(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    pair i turns at f_i / factor * ramp_i + f_i (1 - ramp_i), f_i = theta^(-2i / rotary_dim); cos and sin are
+    multiplied by 0.1 ln(factor) + 1.  ``factor`` None: plain frequencies, no factor on cos and sin."""
+
+    rotary_dim: int
+    theta: float
+    factor: Optional[float] = None
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+    kind: str = "rope_scaled"
+
+
+@dataclass(frozen=True)
 class NoPositionSpec:
     """Queries and keys are used as projected."""
 
@@ -122,6 +139,51 @@ class LatentAttentionSpec:
     norm_eps: float
     prefix: str
     kind: str = "latent_attention"
+    rotary_pairing: str = "adjacent"  # which elements form pair i: "adjacent" (2i, 2i + 1) or "halves" (i, i + dims/2)
+    rotary_scaling: Optional[Tuple[float, float, float, float]] = None  # (factor, original, fast, slow): see ScaledRotarySpec
+    gate_per_head: bool = False  # the output gate is one number a head (g [n_heads, hidden]) instead of one an element
+    sink: Optional[str] = None  # name after <prefix> of a [n_heads] vector: exp(sink_h) joins the softmax's denominator
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec:
+    """Differential attention: every head has two attention maps with queries and keys of their own over the same
+    values; o = rms(a1 - lambda a2) (1 - diff) per head, lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff one number
+    for the layer.  q rows are laid out head by head as [map 1 | map 2] (H * 2 * head_dim), k likewise (G * 2 *
+    head_dim); query head h reads kv head h // (H / G).  ``conv_taps``: a short causal convolution on every channel
+    of q, k and v right behind the projections (None: none).  ``position``: the spec of a rotary part that turns the
+    first rotary_dim elements of each map of each head (None: none).  ``softcap`` c: scaled scores pass through
+    c tanh(s / c).  Tensors after <prefix>: q, k, v, (q.conv, k.conv, v.conv), lq1, lk1, lq2, lk2, o."""
+
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    value_dim: int
+    diff: float
+    scale: float
+    softcap: Optional[float]
+    conv_taps: Optional[int]
+    position: Optional[object]
+    norm_eps: float
+    prefix: str
+    kind: str = "differential_attention"
+
+
+@dataclass(frozen=True)
+class MlstmSpec:
+    """Matrix memory of an mLSTM: per head a state S [head_dim, value_dim], a normaliser and the running maximum of
+    the gates' logarithms (``parts.linear_state.Mlstm``).  Tensors after <prefix>: q, k, v, g, o, norm [H * V],
+    i [H, hidden], i.b, f [H, hidden], f.b."""
+
+    hidden: int
+    n_heads: int
+    head_dim: int
+    value_dim: int
+    gate_cap: float
+    norm_eps: float
+    prefix: str
+    kind: str = "mlstm"
 
 
 @dataclass(frozen=True)
@@ -205,6 +267,7 @@ class DenseMlpSpec:
     kind: str = "swiglu_mlp"
     activation: str = "silu"  # what the gate passes through: silu or relu
     tensor_names: Optional[Tuple[str, str, str]] = None  # (gate, up, down) after <prefix>, if spelled differently
+    bias_names: Optional[Tuple[str, str, str]] = None  # (gate, up, down) biases after <prefix>; None: no biases
 
 
 @dataclass(frozen=True)
@@ -240,6 +303,14 @@ class MoeSpec:
     # names after <prefix> where a checkpoint spells them differently: (router, expert pattern with {e} and {part},
     # shared pattern with {part}), part being gate, up or down
     tensor_names: Optional[Tuple[str, str, str]] = None
+    # experts without a gate: down(act(up x)) with act one of the plain products' activations (e.g. "relu_square");
+    # None: gated experts.  The shared expert has the same form.
+    plain_activation: Optional[str] = None
+    choice_bias: Optional[str] = None  # name after <prefix> of a [n_experts] vector added to the scores for the CHOICE
+    #                                    only (sigmoid scores); the weights use the scores without it
+    weight_scale: float = 1.0  # the final weights are multiplied by this
+    renorm_eps: float = 0.0  # added to the sum the kept scores are divided by (norm_topk_prob)
+    shared_gate_name: Optional[str] = None  # name after <prefix> of the shared expert's [1, hidden] gate row
 
 
 @dataclass(frozen=True)
@@ -264,6 +335,9 @@ class ParallelBlockSpec:
     mixer: object
     ffn: Optional[object]
     kind: str = "parallel"
+    # h += residual_mult * (mixer(norm1(h)) + ffn(norm1(h))): the sum of the sublayers is made in a 32-bit buffer,
+    # multiplied and added (1.0: the sublayers add to the stream themselves)
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -309,6 +383,7 @@ class ModelSpec:
     logit_scale: float = 1.0  # the head's output is multiplied by this
     position_table: Optional[str] = None  # a learned [max_positions, hidden] table: row p is added to position p's embedding
     logit_softcap: Optional[float] = None  # c: the logits pass through c * tanh(z / c)
+    embedding_scale: float = 1.0  # the embedding rows are multiplied by this
 
     @property
     def n_caches(self) -> int:
