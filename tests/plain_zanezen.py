@@ -7,9 +7,28 @@ tests compare the engine with it.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
+
+_ROUND = None      # an element type that everything the design allows in 16 bits is rounded to (None: nothing is)
+
+
+@contextlib.contextmanager
+def rounded_to(dtype):
+    """Inside: the products' inputs and outputs that an engine may keep in ``dtype`` are rounded to it, so that the
+    distance to the unrounded result shows what rounding alone does."""
+    global _ROUND
+    old, _ROUND = _ROUND, dtype
+    try:
+        yield
+    finally:
+        _ROUND = old
+
+
+def _r(x):
+    return x.to(_ROUND).to(x.dtype) if _ROUND is not None else x
 
 
 def rms(x, eps):
@@ -94,21 +113,22 @@ def mlstm(m, W, p, h, eps):
             out[t, a] = (S.T @ q[t, a]) / den
     y = rms(out, eps).reshape(n, H * V) * W[p + "norm"]
     y = y * torch.sigmoid(h @ W[p + "g"].T)
-    return y @ W[p + "o"].T
+    return _r(y) @ W[p + "o"].T
 
 
 def differential_attention(m, W, p, h, eps):
     """Two attention maps a head over the same values; the second is taken off the first, times lambda."""
     n = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q, k, v = h @ W[p + "q"].T, h @ W[p + "k"].T, h @ W[p + "v"].T
+    q, k, v = _r(h @ W[p + "q"].T), _r(h @ W[p + "k"].T), _r(h @ W[p + "v"].T)
     if m.get("conv"):
         q, k, v = short_conv(q, W[p + "q.conv"]), short_conv(k, W[p + "k.conv"]), short_conv(v, W[p + "v.conv"])
-    q, k, v = q.view(n, H, 2, D), k.view(n, G, 2, D), v.view(n, G, V)
+    q, k, v = q.view(n, H, 2, D), k.view(n, G, 2, D), _r(v).view(n, G, V)
     rot = m.get("rot")
     if rot and rot.get("dims"):
         f, mag = rotary_frequencies(rot["dims"], float(rot["base"]), rot.get("scaling"))
         q, k = rotate_halves(q, rot["dims"], f, mag), rotate_halves(k, rot["dims"], f, mag)
+    q, k = _r(q), _r(k)
     lam = (torch.exp((W[p + "lq1"] * W[p + "lk1"]).sum()) - torch.exp((W[p + "lq2"] * W[p + "lk2"]).sum())
            + float(m["diff"]))
     ok = causal(n)
@@ -121,9 +141,9 @@ def differential_attention(m, W, p, h, eps):
             if m.get("softcap"):
                 s = capped(s, float(m["softcap"]))
             s = s.masked_fill(~ok, float("-inf"))
-            maps.append(torch.softmax(s, dim=-1) @ v[:, g])
+            maps.append(_r(torch.softmax(s, dim=-1) @ v[:, g]))
         out[:, a] = rms(maps[0] - lam * maps[1], eps) * (1.0 - float(m["diff"]))
-    return out.reshape(n, H * V) @ W[p + "o"].T
+    return _r(out.reshape(n, H * V)) @ W[p + "o"].T
 
 
 def latent_attention(m, W, p, h, eps):
@@ -131,17 +151,17 @@ def latent_attention(m, W, p, h, eps):
     learned number per head in the softmax's denominator; a gate per head."""
     n = h.shape[0]
     H, D, R, V, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    q = (h @ W[p + "q"].T).view(n, H, D + R)
-    dkv = h @ W[p + "dkv"].T
-    c = rms(dkv[:, :C], eps) * W[p + "dkv.norm"]
+    q = _r(h @ W[p + "q"].T).view(n, H, D + R)
+    dkv = _r(h @ W[p + "dkv"].T)
+    c = _r(rms(dkv[:, :C], eps) * W[p + "dkv.norm"])
     kr = dkv[:, C:]
     rot = m["rot"]
     f, mag = rotary_frequencies(rot["dims"], float(rot["base"]), rot.get("scaling"))
     q_rot = rotate_halves(q[:, :, D:], rot["dims"], f, mag)
-    kr = rotate_halves(kr, rot["dims"], f, mag)
+    q_rot, kr = _r(q_rot), _r(rotate_halves(kr, rot["dims"], f, mag))
     k = (c @ W[p + "uk"].T).view(n, H, D)
     v = (c @ W[p + "uv"].T).view(n, H, V)
-    gate = torch.sigmoid(h @ W[p + "g"].T)                     # [n, H]
+    gate = torch.sigmoid(_r(h @ W[p + "g"].T))                 # [n, H]
     ok = causal(n)
     out = torch.zeros(n, H, V, dtype=h.dtype)
     for a in range(H):
@@ -152,17 +172,17 @@ def latent_attention(m, W, p, h, eps):
         e = torch.exp(s - mx)
         w = e / (e.sum(dim=-1, keepdim=True) + torch.exp(sink - mx))
         out[:, a] = (w @ v[:, a]) * gate[:, a:a + 1]
-    return out.reshape(n, H * V) @ W[p + "o"].T
+    return _r(out.reshape(n, H * V)) @ W[p + "o"].T
 
 
 def dense_mlp(W, p, h):
-    g = h @ W[p + "gate"].T + W[p + "gate.b"]
-    u = h @ W[p + "up"].T + W[p + "up.b"]
-    return (torch.nn.functional.silu(g) * u) @ W[p + "down"].T + W[p + "down.b"]
+    g = _r(h @ W[p + "gate"].T + W[p + "gate.b"])
+    u = _r(h @ W[p + "up"].T + W[p + "up.b"])
+    return _r(torch.nn.functional.silu(g) * u) @ W[p + "down"].T + W[p + "down.b"]
 
 
 def expert(W, p, h):
-    return torch.relu(h @ W[p + "up"].T) ** 2 @ W[p + "down"].T
+    return _r(_r(torch.relu(h @ W[p + "up"].T) ** 2) @ W[p + "down"].T)
 
 
 def choose_experts(f, W, p, h):
@@ -203,11 +223,11 @@ def forward(cfg, W, tokens, return_layers=False, return_margins=False):
     """Logits [n, vocab] of one sequence (and the residual stream after every layer, the routers' smallest margins)."""
     eps = float(cfg["norm"]["eps"])
     mult = float(cfg.get("residual_mult", 1.0))
-    x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(cfg["embedding"]["scale"])
+    x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     layers, margins = [], torch.full((len(tokens),), float("inf"), dtype=x.dtype)
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
-        h = rms(x, eps) * W[p + "norm1"]
+        h = _r(rms(x, eps) * W[p + "norm1"])
         y = MIXERS[layer["type"]](layer["mixer"], W, p + "mix.", h, eps)
         f = layer.get("mlp")
         if f is not None:
@@ -218,7 +238,7 @@ def forward(cfg, W, tokens, return_layers=False, return_margins=False):
                 margins = torch.minimum(margins, router_margins(f, W, p + "mlp.", h))
         x = x + mult * y
         layers.append(x)
-    logits = (rms(x, eps) * W["final.norm"]) @ W["head"].T
+    logits = _r(rms(x, eps) * W["final.norm"]) @ W["head"].T
     out = (logits,)
     if return_layers:
         out += (torch.stack(layers),)
