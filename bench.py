@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape a2.7b|a14b] [--repeats 3]
     python bench.py --designs        (the Safepel design beside the dense decoder at equal sizes; its own JSON line)
     python bench.py --designs bobepel   (the Bobepel design beside the Qwen2-MoE decoder at equal sizes)
+    python bench.py --designs zanezen   (the Zanezen design beside Bobepel at equal sizes)
 
 Default workload: the layer sizes of the Qwen1.5-MoE-A2.7B shape (24 layers, hidden
 2048, 16 heads of 128, 60 experts top-4 of width 1408, shared expert 5632, vocab
@@ -235,6 +236,35 @@ def sesuzen_shape(width, layers, ff, vocab=32768, window=1024, moe=False):
             "layers": [delta if i % 2 == 0 else att for i in range(layers)]}
 
 
+def zanezen_shape(width, layers, vocab=32768):
+    """Layer sizes that resemble a real model's: mLSTM layers with heads of 128 x 128, differential attention with two
+    maps of 64 a head and values of 128 on a quarter as many key heads (four taps, 32 rotated elements a map at
+    stretched frequencies, capped scores), latent attention as in the Bobepel shape (a latent of 512 with 64 rotated
+    elements, a sink and a gate per head), in turn mLSTM, attention, attention, latent.  60 experts of which a token
+    uses 4 behind the first attention and the latent layer; their two matrices hold what the Bobepel shape's three
+    hold (1.5 times the width), the shared expert likewise; the dense feed-forward of the other layers is as wide as
+    the experts a token visits."""
+    h = width // 128
+    ff = width * 11 // 16 // 64 * 64
+    wide = 3 * ff // 2 // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": wide}, "router": {"experts": 60, "top": 4, "scale": 2.5}, "shared": {"ff": 4 * wide}}
+    dense = {"kind": "dense", "ff": 8 * ff}
+    mlstm = {"type": "mlstm", "mixer": {"heads": h, "dim": 128, "vdim": 128, "gate_cap": 15.0}, "mlp": dense}
+
+    def att(mlp):
+        return {"type": "attention", "mlp": mlp, "mixer": {
+            "heads": h, "kv_heads": max(1, h // 4), "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.5, "softcap": 30.0,
+            "conv": 4, "rot": {"dims": 32, "base": 1000000.0,
+                               "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+
+    lat = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": h, "dim": 128, "rot_dim": 64, "rot": {"dims": 64, "base": 1000000.0}, "vdim": 128, "kv_rank": 512,
+        "scale": 192 ** -0.5}}
+    return {"architecture": "Zanezen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": CONTEXT,
+            "embedding": {"scale": float(width) ** 0.5}, "residual_mult": 0.5,
+            "layers": [(mlstm, att(moe), att(dense), lat)[i % 4] for i in range(layers)]}
+
+
 def compare_designs(args) -> int:
     """Prefill and decode throughput of a design and of the closest existing decoder at a few equal sizes (random
     bfloat16 weights), with the device time of every class of kernel from a traced pass beside them."""
@@ -352,6 +382,15 @@ def compare_designs(args) -> int:
                           "prompt_tokens": PREFILL_TOKENS, "decode_steps_timed": steps, "peaks": pk,
                           "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "sizes": rows}))
         return 0
+    if args.designs == "zanezen":
+        for width, layers, _ in sizes:
+            a, b = zanezen_shape(width, layers), bobepel_shape(width, layers)
+            rows.append({"width": width, "layers": layers, "expert_ff": a["layers"][1]["mlp"]["expert"]["ff"],
+                         "zanezen": measure(a), "bobepel": measure(b)})
+        print(json.dumps({"designs": "Zanezen beside Bobepel at equal size", "dtype": "bf16", "batch": batch,
+                          "prompt_tokens": PREFILL_TOKENS, "decode_steps_timed": steps, "peaks": pk,
+                          "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "sizes": rows}))
+        return 0
     if args.designs == "bobepel":
         for width, layers, _ in sizes:
             a, b = bobepel_shape(width, layers), moe_like(width, layers)
@@ -384,11 +423,11 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps steps each; the median counts")
-    ap.add_argument("--designs", nargs="?", const="safepel", default=None, choices=["safepel", "bobepel", "sesuzen", "sesuzen-moe"],
+    ap.add_argument("--designs", nargs="?", const="safepel", default=None, choices=["safepel", "bobepel", "sesuzen", "sesuzen-moe", "zanezen"],
                     help="instead of the default workload: prefill and decode of a design beside the closest existing "
                          "decoder at a few equal sizes, with device time per class of kernel (safepel: beside the dense "
                          "Qwen2 decoder; bobepel: beside the Qwen2-MoE decoder; sesuzen: dense feed-forwards, beside "
-                         "Safepel; sesuzen-moe: experts, beside the Qwen2-MoE decoder without its shared expert)")
+                         "Safepel; sesuzen-moe: experts, beside the Qwen2-MoE decoder without its shared expert; zanezen: beside Bobepel)")
     ap.add_argument("--widths", default="", help="--designs: only these widths (commas), e.g. 2048")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -81,6 +81,8 @@ int fx_router_topk(const float* logits, long ld, int n_tokens, int n_experts, in
 int fx_moe_align(const int* ids, int n_tokens, int top_k, int n_experts, int* scratch, int* offsets, int* src_token,
                  int* inv_perm, int* active, int n_slots, void* stream);
 
+// The four product kernels below, gated form with a bias: `bias` holds the gate rows' values at [0, N) and the up
+// rows' at [gate_up_offset, gate_up_offset + N): C = act(gate + b_gate) * (up + b_up).
 int fx_gemm_tc(const void* X, long ldx, const void* W, long ldw, long w_group_stride, int w_rows, const void* bias,
                int bias_dtype, void* C, int c_dtype, long ldc, int accumulate, int M, int N, int K, int gated,
                int gate_up_offset, float act_limit, float act_alpha, const int* group_offsets, int n_groups, int* status,

@@ -201,6 +201,8 @@ __global__ void __launch_bounds__(NTHREADS) skinny_kernel(SkinnyArgs a)
                     if (GATED) up += red[w][1][j][f][tn];
                 }
                 if (a.bias) v += load_any(a.bias, a.bias_dtype, n);
+                // (a gated product's bias holds the gate rows' values, then at gate_up_offset the up rows')
+                if (MODE == 1 && a.bias) up += load_any(a.bias, a.bias_dtype, a.gate_up_offset + n);
                 if (MODE == 1) v = a.act == 2 ? fx_clamped_glu<false>(v, up, a.act_limit, a.act_alpha)
                                                : (a.act ? fmaxf(v, 0.f) : v / (1.0f + expf(-v))) * up;
                 else if (a.act) v = fx_unary(v, a.act);     // a plain product with an activation on its result

@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
     __shared__ int abort_flag_s;
     __shared__ uint32_t tmem_base_s;
     __shared__ __align__(16) float bias_s[4][OUT_N];   // each epilogue warp keeps the tile's bias for itself
+    __shared__ __align__(16) float bias_up_s[GATED ? 4 : 1][GATED ? OUT_N : 1];   // gated: the up rows' bias (behind the gate rows')
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (a.N + OUT_N - 1) / OUT_N;
@@ -231,6 +232,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                 __syncwarp();
                 for (int j = lane; j < OUT_N; j += 32)
                     bias_s[quad][j] = tc.n0 + j < a.N ? load_any(a.bias, a.bias_dtype, tc.n0 + j) : 0.f;
+                if (GATED)      // a gated product's bias holds the gate rows' values, then at gate_up_offset the up rows'
+                    for (int j = lane; j < OUT_N; j += 32)
+                        bias_up_s[quad][j] = tc.n0 + j < a.N ? load_any(a.bias, a.bias_dtype, a.gate_up_offset + tc.n0 + j) : 0.f;
                 __syncwarp();
             }
             // Accumulating into 32-bit rows: the values already there are fetched one chunk ahead, the first chunk
@@ -276,6 +280,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tc_kernel(const __grid_const
                 for (int j = 0; j < 32; ++j) {
                     float x = __uint_as_float(r[j]);
                     if (a.bias) x += bias_s[quad][c * 32 + j];
+                    if (GATED && a.bias) u[j] = __float_as_uint(__uint_as_float(u[j]) + bias_up_s[quad][c * 32 + j]);
                     if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
                                            : (a.act ? fmaxf(x, 0.f) : __fdividef(x, 1.0f + __expf(-x))) * __uint_as_float(u[j]);
                     else if (a.act) x = fx_unary(x, a.act);     // a plain product with an activation on its result

@@ -254,6 +254,8 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
             const int f = t.n0 + quad * 32 + lane;
             const bool f_ok = f < a.N;
             const float bias = (a.bias && f_ok && a.k_splits <= 1) ? load_any(a.bias, a.bias_dtype, f) : 0.f;
+            // (a gated product's bias holds the gate rows' values, then at gate_up_offset the up rows')
+            const float bias_up = (GATED && a.bias && f_ok) ? load_any(a.bias, a.bias_dtype, a.gate_up_offset + f) : 0.f;
             const int n_chunks = (cols_of<TNB>(t) + 31) / 32;
             const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full_bar(buf), (uint32_t)((it / C::NBUF) & 1), abort_flag));
             if (!ok) break;
@@ -276,6 +278,7 @@ __global__ void __launch_bounds__(NTHREADS, (TNB <= 32 ? 2 : 1)) gemm_tc_swap_ke
                 for (int j = 0; j < 32; ++j) {
                     if (row0 + j >= t.row_end) break;
                     float x = __uint_as_float(r[j]) + bias;
+                    if (GATED) u[j] = __float_as_uint(__uint_as_float(u[j]) + bias_up);
                     if (GATED) x = a.act == 2 ? fx_clamped_glu<true>(x, __uint_as_float(u[j]), a.act_limit, a.act_alpha)
                                            : (a.act ? fmaxf(x, 0.f) : x / (1.0f + __expf(-x))) * __uint_as_float(u[j]);
                     else if (a.act) x = fx_unary(x, a.act);     // a plain product with an activation on its result

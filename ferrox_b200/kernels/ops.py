@@ -1309,22 +1309,24 @@ def linear(x, w, out, *, bias=None, accumulate=False, status=None, stream=None, 
     return _apply_unary_(out, act, stream) if act else out
 
 
-def gated_linear(x, w_gu, out, *, status=None, stream=None, activation="silu"):
-    """out = act(x . gate^T) * (x . up^T) with ``w_gu`` = [gate rows ; up rows] and act SiLU or ReLU
-    (``activation``): picks the kernel as :func:`linear` does; the gate|up intermediate reaches memory only on the
-    CUDA-core path."""
+def gated_linear(x, w_gu, out, *, status=None, stream=None, activation="silu", bias=None):
+    """out = act(x . gate^T (+ b_gate)) * (x . up^T (+ b_up)) with ``w_gu`` = [gate rows ; up rows], ``bias`` =
+    [b_gate ; b_up] or None, and act SiLU or ReLU (``activation``): picks the kernel as :func:`linear` does; the
+    gate|up intermediate reaches memory only on the CUDA-core path."""
     T, I = out.shape
     gated = gated_arg(activation)     # the kernels' argument: 0 plain, 1 SiLU gate, 2 ReLU gate, (3, limit, alpha)
+    if bias is not None and bias.numel() != 2 * I:
+        raise KernelError("gated_linear: the bias holds the gate rows' values, then the up rows'")
     if T <= SKINNY_MAX_TOKENS and tc_ok(x, w_gu) and swap_better(T, 2 * I, x.shape[1]):
-        return gemm_tc_swap(x, w_gu, out, gated=gated, status=status, stream=stream)
+        return gemm_tc_swap(x, w_gu, out, bias=bias, gated=gated, status=status, stream=stream)
     if T <= SKINNY_MAX_TOKENS and skinny_ok(x, w_gu):
-        return gemm_skinny(x, w_gu, out, gated=gated, stream=stream)
+        return gemm_skinny(x, w_gu, out, bias=bias, gated=gated, stream=stream)
     if T > SKINNY_MAX_TOKENS and tc_ok(x, w_gu):
         if w_gu.dim() == 2 and pairs_better(T, I, gated=True):
-            return gemm_tc2(x, w_gu, out, gated=gated, status=status, stream=stream)
-        return gemm_tc(x, w_gu, out, gated=gated, status=status, stream=stream)
+            return gemm_tc2(x, w_gu, out, bias=bias, gated=gated, status=status, stream=stream)
+        return gemm_tc(x, w_gu, out, bias=bias, gated=gated, status=status, stream=stream)
     gu = torch.empty(T, 2 * I, dtype=out.dtype, device=out.device)
-    gemm(x, w_gu, gu, stream=stream)
+    gemm(x, w_gu, gu, bias=bias, stream=stream)
     return silu_mul(gu, out, stream=stream, activation=activation)
 
 

@@ -17,8 +17,8 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 class SwigluMlp(FeedForward):
     """down( act(gate x) * (up x) ); ``spec.activation`` names act (SiLU unless the spec says ReLU).  With
-    ``spec.bias_names`` every projection has a bias: down( act(gate x + bg) * (up x + bu) ) + bd; the first product
-    then writes [gate | up] with its bias and one kernel applies the gate."""
+    ``spec.bias_names`` every projection has a bias: down( act(gate x + bg) * (up x + bu) ) + bd; the products'
+    epilogues add them."""
 
     graph_safe = True
 
@@ -60,14 +60,9 @@ class SwigluMlp(FeedForward):
     def forward_into(self, x, out, batch, accumulate=False):
         T, I = x.shape[0], self.spec.intermediate
         act = self.rt.empty(T, I)
-        if self.b_gu is not None:
-            # biases: [gate | up] with its bias from the product's epilogue, then act(gate) * up
-            gu = self.rt.empty(T, 2 * I)
-            ops.linear(x, self.w_gu, gu, bias=self.b_gu, status=batch.status, stream=batch.stream)
-            ops.silu_mul(gu, act, stream=batch.stream, activation=self.activation)
-        else:
-            # act(gate) * up in the epilogue
-            ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream, activation=self.activation)
+        # act(gate (+ bias)) * (up (+ bias)) in the epilogue
+        ops.gated_linear(x, self.w_gu, act, status=batch.status, stream=batch.stream, activation=self.activation,
+                         bias=self.b_gu)
         ops.linear(act, self.w_down, out, bias=self.b_down, accumulate=accumulate, status=batch.status,
                    stream=batch.stream)
 

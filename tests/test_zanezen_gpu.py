@@ -308,7 +308,7 @@ def test_gated_feed_forward_with_biases_alone(dtype):
             w["f." + n] = (w["f." + n].float() * 5).to(torch.bfloat16)
         part, rt = load_part(spec, w, dt)
         wf = floats(w)
-        for T in (1, 3, 20, 70, 300):     # the decode-sized and the prompt-sized kernels
+        for T in (1, 3, 20, 70, 300, 2304):     # the decode-sized and the prompt-sized kernels, pairs of SMs
             x = torch.randn(T, hidden, generator=torch.Generator().manual_seed(T)).to(dt)
             batch = SimpleNamespace(status=None, stream=ops.stream_ptr())
             out = torch.full((T, hidden), float("nan"), device=DEV)
