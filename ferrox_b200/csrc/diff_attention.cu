@@ -1,7 +1,7 @@
 // What an attention mixer with a short convolution behind its projections does between the fused product and the
 // attention kernel, and what differential attention does after it.
 //
-// fx_conv_rotary_store, one block a token.  The row as projected is [q heads | k heads | v heads]; on every channel
+// fx_conv_rotary_store, one block a (token, head).  The row as projected is [q heads | k heads | v heads]; on every channel
 //
 //   y_t[c] = sum_j w[c, j] u_(t - taps + 1 + j)[c]          (zeros before the request's start; no input added)
 //
@@ -24,7 +24,7 @@ namespace {
 constexpr int MAX_TAPS = 16;
 
 template <typename T>
-__global__ void __launch_bounds__(256) conv_rotary_store_kernel(
+__global__ void __launch_bounds__(128) conv_rotary_store_kernel(
     const T* __restrict__ proj, long ldp, const void* __restrict__ w, int w_dtype, int taps, float* tail,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
     const float* __restrict__ cos_sin, int rot_dims, int pairing, T* __restrict__ q_out, long ldq,
@@ -32,12 +32,16 @@ __global__ void __launch_bounds__(256) conv_rotary_store_kernel(
     int page_size, int n_q_heads, int n_k_heads, int head_dim, int n_v_heads, int value_dim, int write_cache,
     int update_tail, int* __restrict__ status)
 {
+    // one block a (token, head): q heads, then k heads, then v heads
     fx_pdl_wait();
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, head = blockIdx.y;
     const int b = token_seq[t];
     const int pos = positions[t];
     const int slot = seq_slot[b];
     const int qk = (n_q_heads + n_k_heads) * head_dim, C = qk + n_v_heads * value_dim;
+    const bool is_v = head >= n_q_heads + n_k_heads;
+    const int width = is_v ? value_dim : head_dim;
+    const int c0 = is_v ? qk + (head - n_q_heads - n_k_heads) * value_dim : head * head_dim;    // the head's first channel
     // how many rows before t belong to the same entry (at most taps - 1 matter)
     int own = 0;
     while (own < taps - 1 && t - own - 1 >= 0 && token_seq[t - own - 1] == b) ++own;
@@ -54,53 +58,37 @@ __global__ void __launch_bounds__(256) conv_rotary_store_kernel(
         }
         return acc;
     };
-    long k_base = -1, v_base = -1;
-    if (write_cache) {
+    T* dst = nullptr;      // where the head's elements go
+    if (head < n_q_heads) {
+        dst = q_out + (long)t * ldq + (long)head * head_dim;
+    } else if (write_cache) {
         const int page = block_table[(long)slot * table_width + pos / page_size];
         if (page < 0) { if (threadIdx.x == 0 && status) atomicExch(status, 2); }
-        else {
-            k_base = ((long)page * n_k_heads * page_size + (pos % page_size)) * head_dim;
-            v_base = ((long)page * n_v_heads * page_size + (pos % page_size)) * value_dim;
-        }
+        else if (is_v) dst = v_pages + (((long)page * n_v_heads + (head - n_q_heads - n_k_heads)) * page_size + (pos % page_size)) * value_dim;
+        else dst = k_pages + (((long)page * n_k_heads + (head - n_q_heads)) * page_size + (pos % page_size)) * head_dim;
     }
-    const int half = rot_dims >> 1;
-    const float* cs = cos_sin ? cos_sin + (long)t * half * 2 : nullptr;
-    // q and k heads: element i of head h; the first of a rotated pair does both, its partner is skipped
-    for (int idx = threadIdx.x; idx < qk; idx += blockDim.x) {
-        const int h = idx / head_dim, i = idx - h * head_dim;
-        float y0, y1 = 0.f;
-        int i0 = i, i1 = -1;
-        if (i < rot_dims && cs) {
-            const int p = pairing ? i >> 1 : i;
-            if (pairing ? (i & 1) : (i >= half)) continue;
-            i1 = pairing ? i + 1 : i + half;
-            const float a = conv(idx), bb = conv(idx - i + i1), c = cs[2 * p], s = cs[2 * p + 1];
-            y0 = a * c - bb * s;
-            y1 = bb * c + a * s;
-        } else {
-            y0 = conv(idx);
-        }
-        if (h < n_q_heads) {
-            T* o = q_out + (long)t * ldq + (long)h * head_dim;
-            o[i0] = from_f32<T>(y0);
-            if (i1 >= 0) o[i1] = from_f32<T>(y1);
-        } else if (k_base >= 0) {
-            T* o = k_pages + k_base + (long)(h - n_q_heads) * page_size * head_dim;
-            o[i0] = from_f32<T>(y0);
-            if (i1 >= 0) o[i1] = from_f32<T>(y1);
-        }
-    }
-    if (v_base >= 0) {
-        for (int idx = threadIdx.x; idx < n_v_heads * value_dim; idx += blockDim.x) {
-            const int h = idx / value_dim, i = idx - h * value_dim;
-            v_pages[v_base + (long)h * page_size * value_dim + i] = from_f32<T>(conv(qk + idx));
+    const int rot = (is_v || !cos_sin) ? 0 : rot_dims, half = rot >> 1;
+    const float* cs = cos_sin ? cos_sin + (long)t * (rot_dims >> 1) * 2 : nullptr;
+    if (dst) {
+        // element i of the head; the first of a rotated pair does both, its partner is skipped
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            if (i < rot) {
+                if (pairing ? (i & 1) : (i >= half)) continue;
+                const int p = pairing ? i >> 1 : i, i1 = pairing ? i + 1 : i + half;
+                const float a = conv(c0 + i), bb = conv(c0 + i1), c = cs[2 * p], s = cs[2 * p + 1];
+                dst[i] = from_f32<T>(a * c - bb * s);
+                dst[i1] = from_f32<T>(bb * c + a * s);
+            } else {
+                dst[i] = from_f32<T>(conv(c0 + i));
+            }
         }
     }
     if (update_tail && taps > 1) {
-        // (the caller's promise that every entry brings exactly one token: this block is the only reader of the slot's
-        // tail in the whole step, and moves it on by the token's own row once all its sums are made)
+        // (the caller's promise that every entry brings exactly one token: this block is the only reader of its
+        // channels' tail in the whole step, and moves it on by the token's own row once all its sums are made)
         __syncthreads();
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const int c = c0 + i;
             for (int j = 0; j + 1 < taps - 1; ++j) tl[(long)j * C + c] = tl[(long)(j + 1) * C + c];
             tl[(long)(taps - 2) * C + c] = to_f32(row[c]);
         }
@@ -147,8 +135,11 @@ extern "C" int fx_conv_rotary_store(const void* proj, int dtype, long ldp, const
         n_v_heads <= 0 || proj == q_out)
         return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_tokens, n_q_heads + n_k_heads + n_v_heads);
+    const int widest = head_dim > value_dim ? head_dim : value_dim;
+    const int nt = widest <= 32 ? 32 : widest <= 64 ? 64 : 128;
 #define FX_GO(T)                                                                                                      \
-    fx_launch_pdl(conv_rotary_store_kernel<T>, n_tokens, 256, 0, s, (const T*)proj, ldp, w, w_dtype, taps, tail,      \
+    fx_launch_pdl(conv_rotary_store_kernel<T>, grid, nt, 0, s, (const T*)proj, ldp, w, w_dtype, taps, tail,           \
                   positions, token_seq, seq_slot, cos_sin, rot_dims, pairing, (T*)q_out, ldq, (T*)k_pages,            \
                   (T*)v_pages, block_table, table_width, page_size, n_q_heads, n_k_heads, head_dim, n_v_heads,        \
                   value_dim, write_cache, update_tail, status)

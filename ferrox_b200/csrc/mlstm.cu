@@ -8,14 +8,15 @@
 //   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
 //
 // over the tokens of every entry of the step, in order, whatever the cut.  A column of S (one value index) never
-// meets another: a group of R lanes owns one column for the whole step, its rows in registers (lane p holds rows
-// p, p + R, ...); every lane also carries the rows of n that match its rows of S, so that n . q comes out of the
+// meets another: a group of R lanes owns one column for the whole step, its rows in registers (in runs of four);
+// every lane also carries the rows of n that match its rows of S, so that n . q comes out of the
 // same pass.  n and m are the same for every column; so that no block reads what another has already moved on,
 // each block of columns (blockIdx.z) keeps a copy of its own of both in the state: n [slots, H, Z, D] and
 // m [slots, H, Z] with Z = fx_mlstm_column_blocks(D, V), all copies equal.  Tokens are
-// staged CH at a time in shared memory: the gates of the chunk's tokens are worked out by one thread each, the
-// chain of maxima by one thread, the three exponentials of a token by one thread each, so that the loop over the
-// tokens holds multiply-adds only.  Everything is 32-bit; the products that made q, k, v and the gates' inputs
+// staged CH at a time in shared memory (the next chunk's rows travel into registers meanwhile): the first warp works
+// out the chunk's gates (a lane a token), runs the chain of maxima over shuffles and takes the three exponentials
+// of every token, so that the loop over the tokens holds multiply-adds only; the read-outs' reductions over a
+// column's lanes are made for the whole chunk together.  Everything is 32-bit; the products that made q, k, v and the gates' inputs
 // were written in 32 bits.
 //
 // State layout: S [slots, H, V, D] (column by column), n [slots, H, Z, D], m [slots, H, Z]; zeroed at admission.
@@ -53,13 +54,17 @@ struct MlstmArgs {
     int n_tokens, H, D, V, R;
 };
 
-template <int RPL>
+// Rows in runs of four: lane p of a column holds rows 4 R (i / 4) + 4 p + (i % 4), i < RPL, so that k and q are
+// read from shared memory in conflict-free 16-byte pieces.  DP = R * RPL >= D is the padded height (zeros beyond D).
+// PRE: elements of every k and q row of the next chunk that a thread brings into registers while this chunk is
+// worked on (1: DP <= 128, 2: DP <= 256); 0: the rows are read when they are staged.
+template <int RPL, int PRE>
 __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs a)
 {
-    __shared__ float k_s[CH][MAX_D];
-    __shared__ float q_s[CH][MAX_D];
+    __shared__ __align__(16) float k_s[CH][MAX_D];
+    __shared__ __align__(16) float q_s[CH][MAX_D];
     __shared__ float v_s[CH][ML_THREADS];
-    __shared__ float gi_s[CH], gf_s[CH], keep_s[CH], take_s[CH], floor_s[CH], m_s[CH + 1];
+    __shared__ float keep_s[CH], take_s[CH], floor_s[CH];
     fx_pdl_wait_only();
     const int b = blockIdx.x, h = blockIdx.y;
     const int R = a.R, cols = ML_THREADS / R;
@@ -67,7 +72,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
     const int col0 = blockIdx.z * cols, col = col0 + cl;
     const int r0 = first_row_of(a.token_seq, a.n_tokens, b), r1 = first_row_of(a.token_seq, a.n_tokens, b + 1);
     if (r1 <= r0) return;
-    const int D = a.D, V = a.V, H = a.H;
+    const int D = a.D, V = a.V, H = a.H, DP = R * RPL;
     const bool live = col < V;
     const long slot = a.seq_slot[b];
     float* sp = a.S + ((slot * H + h) * V + (live ? col : 0)) * D;
@@ -76,89 +81,171 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
     float S[RPL], N[RPL];
 #pragma unroll
     for (int i = 0; i < RPL; ++i) {
-        const int row = part + i * R;
+        const int row = (i >> 2) * 4 * R + part * 4 + (i & 3);
         S[i] = (live && row < D) ? sp[row] : 0.f;
         N[i] = row < D ? np[row] : 0.f;
     }
-    if (threadIdx.x == 0) m_s[0] = a.m[copy];
+    float m_run = a.m[copy];      // the running maximum (warp 0 moves it on; thread 0 writes it back)
     const float bi = load_any(a.i_bias, a.bias_dtype, h), bf = load_any(a.f_bias, a.bias_dtype, h);
     const float inv_cap = 1.0f / a.cap;
+    const float* Kp = a.k + (long)h * D;
+    const float* Qp = a.q + (long)h * D;
+    const float* Vp = a.v + (long)h * V + col0;
 
+    // what a thread brings of a chunk: elements t and t + 128 of every token's k and q row, two of the chunk's
+    // values, and (threads below CH) one token's gate inputs; all loads are unconditional, from indices clamped into
+    // the chunk, so that they are issued together
+    float kr[PRE ? PRE * CH : 1], qr[PRE ? PRE * CH : 1], vr[2], gir = 0.f, gfr = 0.f;
+    const int i0 = min((int)threadIdx.x, D - 1), i1 = min((int)threadIdx.x + ML_THREADS, D - 1);
+    auto fetch = [&](int c0, int nt) {
+        if (PRE) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                const long t = c0 + min(tt, nt - 1);
+                kr[tt] = __ldg(Kp + t * a.ldk + i0);
+                qr[tt] = __ldg(Qp + t * a.ldq + i0);
+            }
+            if (PRE == 2) {
+#pragma unroll
+                for (int tt = 0; tt < CH; ++tt) {
+                    const long t = c0 + min(tt, nt - 1);
+                    kr[CH + tt] = __ldg(Kp + t * a.ldk + i1);
+                    qr[CH + tt] = __ldg(Qp + t * a.ldq + i1);
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int idx = min((int)threadIdx.x + e * ML_THREADS, nt * cols - 1);
+            const int tt = idx / cols, c = min(idx - tt * cols, V - 1 - col0);
+            vr[e] = __ldg(Vp + (long)(c0 + tt) * a.ldv + c);
+        }
+        const float* g = a.gates + (long)(c0 + min((int)threadIdx.x, nt - 1)) * a.ldg;
+        gir = __ldg(g + h);
+        gfr = __ldg(g + H + h);
+    };
+    fetch(r0, min(CH, r1 - r0));
     for (int c0 = r0; c0 < r1; c0 += CH) {
         const int nt = min(CH, r1 - c0);
-        __syncthreads();      // the chunk before is done with the staged rows (and m_s[0] is set)
-        for (int idx = threadIdx.x; idx < nt * D; idx += ML_THREADS) {
-            const int tt = idx / D, i = idx - tt * D;
-            k_s[tt][i] = a.k[(long)(c0 + tt) * a.ldk + (long)h * D + i];
-            q_s[tt][i] = a.q[(long)(c0 + tt) * a.ldq + (long)h * D + i] * a.q_scale;
+        __syncthreads();      // the chunk before is done with the staged rows
+        if (threadIdx.x < 32) {
+            // the chunk's gates, the chain of maxima and the three exponentials of every token, by the first warp
+            const int lane = threadIdx.x;
+            const float gi = a.cap * tanhf((gir + bi) * inv_cap);
+            const float gf = logsigmoid_f(a.cap * tanhf((gfr + bf) * inv_cap));
+            float m = m_run, m_before = 0.f, m_after = 0.f;
+            for (int tt = 0; tt < nt; ++tt) {
+                const float f = __shfl_sync(0xffffffffu, gf, tt), i = __shfl_sync(0xffffffffu, gi, tt);
+                const float mn = fmaxf(f + m, i);
+                if (lane == tt) { m_before = m; m_after = mn; }
+                m = mn;
+            }
+            m_run = m;
+            if (lane < nt) {
+                keep_s[lane] = expf(gf + m_before - m_after);
+                take_s[lane] = expf(gi - m_after);
+                floor_s[lane] = expf(-m_after);
+            }
         }
-        for (int idx = threadIdx.x; idx < nt * cols; idx += ML_THREADS) {
-            const int tt = idx / cols, c = idx - tt * cols;
-            v_s[tt][c] = col0 + c < V ? a.v[(long)(c0 + tt) * a.ldv + (long)h * V + col0 + c] : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            const float* g = a.gates + (long)(c0 + threadIdx.x) * a.ldg;
-            gi_s[threadIdx.x] = a.cap * tanhf((g[h] + bi) * inv_cap);
-            gf_s[threadIdx.x] = logsigmoid_f(a.cap * tanhf((g[H + h] + bf) * inv_cap));
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {      // the chain of maxima: an addition and a maximum a token
-            float m = m_s[0];
-            for (int tt = 0; tt < nt; ++tt) { m = fmaxf(gf_s[tt] + m, gi_s[tt]); m_s[tt + 1] = m; }
-        }
-        __syncthreads();
-        if (threadIdx.x < nt) {
-            const int tt = threadIdx.x;
-            keep_s[tt] = expf(gf_s[tt] + m_s[tt] - m_s[tt + 1]);
-            take_s[tt] = expf(gi_s[tt] - m_s[tt + 1]);
-            floor_s[tt] = expf(-m_s[tt + 1]);
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float keep = keep_s[tt], take = take_s[tt], vj = v_s[tt][cl];
-            float num = 0.f, den = 0.f;
+        if (PRE) {
+            const int i = threadIdx.x;
+            if (i < DP) {
 #pragma unroll
-            for (int i = 0; i < RPL; ++i) {
-                const int row = part + i * R;      // rows beyond D hold zeros: their k and q are never read
-                const float kk = row < D ? take * k_s[tt][row] : 0.f;
-                const float qq = row < D ? q_s[tt][row] : 0.f;
-                S[i] = fmaf(kk, vj, keep * S[i]);
-                N[i] = fmaf(keep, N[i], kk);
-                num = fmaf(S[i], qq, num);
-                den = fmaf(N[i], qq, den);
+                for (int tt = 0; tt < CH; ++tt) {
+                    k_s[tt][i] = i < D ? kr[tt] : 0.f;
+                    q_s[tt][i] = i < D ? qr[tt] * a.q_scale : 0.f;
+                }
             }
-            for (int o = R >> 1; o > 0; o >>= 1) {
-                num += __shfl_xor_sync(0xffffffffu, num, o);
-                den += __shfl_xor_sync(0xffffffffu, den, o);
+            if (PRE == 2 && i + ML_THREADS < DP) {
+#pragma unroll
+                for (int tt = 0; tt < CH; ++tt) {
+                    k_s[tt][i + ML_THREADS] = i + ML_THREADS < D ? kr[CH + tt] : 0.f;
+                    q_s[tt][i + ML_THREADS] = i + ML_THREADS < D ? qr[CH + tt] * a.q_scale : 0.f;
+                }
             }
-            if (live && part == 0)
-                a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = num / (fmaxf(fabsf(den), floor_s[tt]) + 1e-6f);
+        } else {
+            for (int idx = threadIdx.x; idx < nt * DP; idx += ML_THREADS) {
+                const int tt = idx / DP, i = idx - tt * DP;
+                k_s[tt][i] = i < D ? Kp[(long)(c0 + tt) * a.ldk + i] : 0.f;
+                q_s[tt][i] = i < D ? Qp[(long)(c0 + tt) * a.ldq + i] * a.q_scale : 0.f;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int idx = threadIdx.x + e * ML_THREADS;
+            if (idx < nt * cols) {
+                const int tt = idx / cols, c = idx - tt * cols;
+                v_s[tt][c] = col0 + c < V ? vr[e] : 0.f;
+            }
         }
         __syncthreads();
-        if (threadIdx.x == 0) m_s[0] = m_s[nt];
+        if (c0 + CH < r1) fetch(c0 + CH, min(CH, r1 - c0 - CH));
+        float num[CH], den[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            num[tt] = den[tt] = 0.f;
+            if (tt < nt) {      // (uniform across the block)
+                const float keep = keep_s[tt], take = take_s[tt], tv = take * v_s[tt][cl];
+                // (four partial sums a dot product: the chain of dependent additions is a quarter as long)
+                float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f, d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < RPL; i += 4) {
+                    const int at = (i >> 2) * 4 * R + part * 4;
+                    const float4 kk = *reinterpret_cast<const float4*>(&k_s[tt][at]);
+                    const float4 qq = *reinterpret_cast<const float4*>(&q_s[tt][at]);
+                    S[i] = fmaf(kk.x, tv, keep * S[i]);             N[i] = fmaf(take, kk.x, keep * N[i]);
+                    S[i + 1] = fmaf(kk.y, tv, keep * S[i + 1]);     N[i + 1] = fmaf(take, kk.y, keep * N[i + 1]);
+                    S[i + 2] = fmaf(kk.z, tv, keep * S[i + 2]);     N[i + 2] = fmaf(take, kk.z, keep * N[i + 2]);
+                    S[i + 3] = fmaf(kk.w, tv, keep * S[i + 3]);     N[i + 3] = fmaf(take, kk.w, keep * N[i + 3]);
+                    n0 = fmaf(S[i], qq.x, n0); n1 = fmaf(S[i + 1], qq.y, n1);
+                    n2 = fmaf(S[i + 2], qq.z, n2); n3 = fmaf(S[i + 3], qq.w, n3);
+                    d0 = fmaf(N[i], qq.x, d0); d1 = fmaf(N[i + 1], qq.y, d1);
+                    d2 = fmaf(N[i + 2], qq.z, d2); d3 = fmaf(N[i + 3], qq.w, d3);
+                }
+                num[tt] = (n0 + n1) + (n2 + n3);
+                den[tt] = (d0 + d1) + (d2 + d3);
+            }
+        }
+        // the read-outs of the chunk: all reductions over a column's lanes together, then the division
+        for (int o = R >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) {
+                num[tt] += __shfl_xor_sync(0xffffffffu, num[tt], o);
+                den[tt] += __shfl_xor_sync(0xffffffffu, den[tt], o);
+            }
+        }
+        if (live && part == 0) {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt)
+                if (tt < nt)
+                    a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = num[tt] / (fmaxf(fabsf(den[tt]), floor_s[tt]) + 1e-6f);
+        }
     }
     fx_pdl_trigger();
     if (live) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
-            const int row = part + i * R;
+            const int row = (i >> 2) * 4 * R + part * 4 + (i & 3);
             if (row < D) sp[row] = S[i];
         }
     }
     if (cl == 0) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
-            const int row = part + i * R;
+            const int row = (i >> 2) * 4 * R + part * 4 + (i & 3);
             if (row < D) np[row] = N[i];
         }
     }
-    if (threadIdx.x == 0) a.m[copy] = m_s[0];
+    if (threadIdx.x == 0) a.m[copy] = m_run;
 }
+
+// rows a lane holds: a multiple of four
+int rows_per_lane(int D, int R) { return (int)fx_cdiv(D, 4 * R) * 4; }
 
 int lanes_for(int D)
 {
     int R = 4;
-    while (R < 32 && (D + R - 1) / R > 32) R <<= 1;
+    while (R < 32 && rows_per_lane(D, R) > 32) R <<= 1;
     return R;
 }
 
@@ -186,18 +273,30 @@ extern "C" int fx_mlstm_scan(const float* q, long ldq, const float* k, long ldk,
     a.i_bias = i_bias; a.f_bias = f_bias; a.bias_dtype = bias_dtype; a.cap = cap; a.q_scale = q_scale;
     a.S = S; a.n = n; a.m = m; a.out = out; a.ldo = ldo; a.token_seq = token_seq; a.seq_slot = seq_slot;
     a.n_tokens = n_tokens; a.H = H; a.D = D; a.V = V; a.R = lanes_for(D);
-    const int rpl = (D + a.R - 1) / a.R;
+    const int rpl = rows_per_lane(D, a.R);
+    if (rpl > 32) return FX_ERR_SIZE;
+    const int dp = a.R * rpl;
+    const int pre = dp <= ML_THREADS ? 1 : dp <= 2 * ML_THREADS ? 2 : 0;      // elements of a row a thread prefetches
     dim3 grid(n_entries, H, fx_mlstm_column_blocks(D, V));
     cudaStream_t s = (cudaStream_t)stream;
     // a prompt's recurrence starts on an empty device (see fx_launch_pdl_if); a decode step's is set up early
     const bool early = n_tokens < 8 * n_entries;
-#define FX_GO(RPL) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL>, grid, ML_THREADS, 0, s, a)
-    if (rpl <= 4) FX_GO(4);
-    else if (rpl <= 8) FX_GO(8);
-    else if (rpl <= 12) FX_GO(12);
-    else if (rpl <= 16) FX_GO(16);
-    else if (rpl <= 24) FX_GO(24);
-    else FX_GO(32);
+#define FX_GO(RPL)                                                                                                    \
+    do {                                                                                                              \
+        if (pre == 1) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 1>, grid, ML_THREADS, 0, s, a);                  \
+        else if (pre == 2) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 2>, grid, ML_THREADS, 0, s, a);             \
+        else fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 0>, grid, ML_THREADS, 0, s, a);                           \
+    } while (0)
+    switch (rpl) {
+        case 4: FX_GO(4); break;
+        case 8: FX_GO(8); break;
+        case 12: FX_GO(12); break;
+        case 16: FX_GO(16); break;
+        case 20: FX_GO(20); break;
+        case 24: FX_GO(24); break;
+        case 28: FX_GO(28); break;
+        default: FX_GO(32); break;
+    }
 #undef FX_GO
     return fx_launch_status();
 }
