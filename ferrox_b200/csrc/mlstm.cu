@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
     __shared__ __align__(16) float q_s[CH][MAX_D];
     __shared__ float v_s[CH][ML_THREADS];
     __shared__ float keep_s[CH], take_s[CH], floor_s[CH];
+    __shared__ float num_s[CH][ML_THREADS], den_s[CH][ML_THREADS];      // a thread's partial read-outs of the chunk
     fx_pdl_wait_only();
     const int b = blockIdx.x, h = blockIdx.y;
     const int R = a.R, cols = ML_THREADS / R;
@@ -180,11 +181,11 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
         }
         __syncthreads();
         if (c0 + CH < r1) fetch(c0 + CH, min(CH, r1 - c0 - CH));
-        float num[CH], den[CH];
-#pragma unroll
-        for (int tt = 0; tt < CH; ++tt) {
-            num[tt] = den[tt] = 0.f;
-            if (tt < nt) {      // (uniform across the block)
+        // (the loop over the tokens is not unrolled: its body is the whole column's update, and eight copies of
+        // it do not fit the instruction cache)
+#pragma unroll 1
+        for (int tt = 0; tt < nt; ++tt) {
+            {
                 const float keep = keep_s[tt], take = take_s[tt], tv = take * v_s[tt][cl];
                 // (four partial sums a dot product: the chain of dependent additions is a quarter as long)
                 float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f, d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
@@ -202,10 +203,13 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
                     d0 = fmaf(N[i], qq.x, d0); d1 = fmaf(N[i + 1], qq.y, d1);
                     d2 = fmaf(N[i + 2], qq.z, d2); d3 = fmaf(N[i + 3], qq.w, d3);
                 }
-                num[tt] = (n0 + n1) + (n2 + n3);
-                den[tt] = (d0 + d1) + (d2 + d3);
+                num_s[tt][threadIdx.x] = (n0 + n1) + (n2 + n3);
+                den_s[tt][threadIdx.x] = (d0 + d1) + (d2 + d3);
             }
         }
+        float num[CH], den[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) { num[tt] = num_s[tt][threadIdx.x]; den[tt] = den_s[tt][threadIdx.x]; }   // (its own writes)
         // the read-outs of the chunk: all reductions over a column's lanes together, then the division
         for (int o = R >> 1; o > 0; o >>= 1) {
 #pragma unroll
@@ -245,7 +249,7 @@ int rows_per_lane(int D, int R) { return (int)fx_cdiv(D, 4 * R) * 4; }
 int lanes_for(int D)
 {
     int R = 4;
-    while (R < 32 && rows_per_lane(D, R) > 32) R <<= 1;
+    while (R < 32 && rows_per_lane(D, R) > 16) R <<= 1;
     return R;
 }
 
@@ -274,7 +278,7 @@ extern "C" int fx_mlstm_scan(const float* q, long ldq, const float* k, long ldk,
     a.S = S; a.n = n; a.m = m; a.out = out; a.ldo = ldo; a.token_seq = token_seq; a.seq_slot = seq_slot;
     a.n_tokens = n_tokens; a.H = H; a.D = D; a.V = V; a.R = lanes_for(D);
     const int rpl = rows_per_lane(D, a.R);
-    if (rpl > 32) return FX_ERR_SIZE;
+    if (rpl > 16) return FX_ERR_SIZE;
     const int dp = a.R * rpl;
     const int pre = dp <= ML_THREADS ? 1 : dp <= 2 * ML_THREADS ? 2 : 0;      // elements of a row a thread prefetches
     dim3 grid(n_entries, H, fx_mlstm_column_blocks(D, V));
@@ -291,11 +295,7 @@ extern "C" int fx_mlstm_scan(const float* q, long ldq, const float* k, long ldk,
         case 4: FX_GO(4); break;
         case 8: FX_GO(8); break;
         case 12: FX_GO(12); break;
-        case 16: FX_GO(16); break;
-        case 20: FX_GO(20); break;
-        case 24: FX_GO(24); break;
-        case 28: FX_GO(28); break;
-        default: FX_GO(32); break;
+        default: FX_GO(16); break;
     }
 #undef FX_GO
     return fx_launch_status();

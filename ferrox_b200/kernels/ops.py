@@ -502,14 +502,14 @@ def general_delta_scan(r, k, v, u, au, w, state, out, token_seq, seq_slot, n_ent
 def mlstm_column_blocks(head_dim: int, value_dim: int) -> int:
     """Blocks of value columns :func:`mlstm_scan` shares a head's state out over: the copies of the normaliser and of
     the running maximum that the state keeps.  A function of the two sizes alone, stated here as the kernel's
-    launcher states it (128 threads a block; 4 lanes a column, doubled while a lane would hold more than 32 rows, rows
+    launcher states it (128 threads a block; 4 lanes a column, doubled while a lane would hold more than 16 rows, rows
     counted in runs of four), so that a cache can be laid out without the library; the launcher refuses a state laid
     out otherwise."""
     D, V = int(head_dim), int(value_dim)
     if not (0 < D <= 512 and V > 0):
         raise KernelError(f"mlstm: heads of {head_dim} x {value_dim} are outside what the recurrence kernel holds")
     lanes = 4
-    while lanes < 32 and -(-D // (4 * lanes)) * 4 > 32:
+    while lanes < 32 and -(-D // (4 * lanes)) * 4 > 16:
         lanes *= 2
     cols = 128 // lanes
     return -(-V // cols)
