@@ -13,9 +13,10 @@
 // same pass.  n and m are the same for every column; so that no block reads what another has already moved on,
 // each block of columns (blockIdx.z) keeps a copy of its own of both in the state: n [slots, H, Z, D] and
 // m [slots, H, Z] with Z = fx_mlstm_column_blocks(D, V), all copies equal.  Tokens are
-// staged CH at a time in shared memory (the next chunk's rows travel into registers meanwhile): the first warp works
-// out the chunk's gates (a lane a token), runs the chain of maxima over shuffles and takes the three exponentials
-// of every token, so that the loop over the tokens holds multiply-adds only; the read-outs' reductions over a
+// staged CH at a time in shared memory (the next chunk's rows travel into registers meanwhile).  A fifth warp owns no
+// column: a chunk ahead of the others it works out the gates (a lane a token), runs the chain of maxima over
+// shuffles and takes the three exponentials of every token, so that the loop over the tokens holds multiply-adds
+// only and never waits for a transcendental; the read-outs' reductions over a
 // column's lanes are made for the whole chunk together.  Everything is 32-bit; the products that made q, k, v and the gates' inputs
 // were written in 32 bits.
 //
@@ -25,7 +26,8 @@
 
 namespace {
 
-constexpr int ML_THREADS = 128;
+constexpr int ML_THREADS = 128;               // threads that own state columns
+constexpr int ML_BLOCK = ML_THREADS + 32;     // and one more warp that works out the gates a chunk ahead
 constexpr int CH = 8;
 constexpr int MAX_D = 512;
 
@@ -59,12 +61,12 @@ struct MlstmArgs {
 // PRE: elements of every k and q row of the next chunk that a thread brings into registers while this chunk is
 // worked on (1: DP <= 128, 2: DP <= 256); 0: the rows are read when they are staged.
 template <int RPL, int PRE>
-__global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs a)
+__global__ void __launch_bounds__(ML_BLOCK) mlstm_scan_kernel(const MlstmArgs a)
 {
     __shared__ __align__(16) float k_s[CH][MAX_D];
     __shared__ __align__(16) float q_s[CH][MAX_D];
     __shared__ float v_s[CH][ML_THREADS];
-    __shared__ float keep_s[CH], take_s[CH], floor_s[CH];
+    __shared__ float keep_s[2][CH], take_s[2][CH], floor_s[2][CH];      // two chunks: the gate warp runs one ahead
     __shared__ float num_s[CH][ML_THREADS], den_s[CH][ML_THREADS];      // a thread's partial read-outs of the chunk
     fx_pdl_wait_only();
     const int b = blockIdx.x, h = blockIdx.y;
@@ -74,7 +76,8 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
     const int r0 = first_row_of(a.token_seq, a.n_tokens, b), r1 = first_row_of(a.token_seq, a.n_tokens, b + 1);
     if (r1 <= r0) return;
     const int D = a.D, V = a.V, H = a.H, DP = R * RPL;
-    const bool live = col < V;
+    const bool worker = threadIdx.x < ML_THREADS;      // the last warp owns no column
+    const bool live = worker && col < V;
     const long slot = a.seq_slot[b];
     float* sp = a.S + ((slot * H + h) * V + (live ? col : 0)) * D;
     const long copy = (slot * H + h) * gridDim.z + blockIdx.z;      // this block's copy of n and m
@@ -84,9 +87,9 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
     for (int i = 0; i < RPL; ++i) {
         const int row = (i >> 2) * 4 * R + part * 4 + (i & 3);
         S[i] = (live && row < D) ? sp[row] : 0.f;
-        N[i] = row < D ? np[row] : 0.f;
+        N[i] = (worker && row < D) ? np[row] : 0.f;
     }
-    float m_run = a.m[copy];      // the running maximum (warp 0 moves it on; thread 0 writes it back)
+    float m_run = a.m[copy];      // the running maximum (the gate warp moves it on and writes it back)
     const float bi = load_any(a.i_bias, a.bias_dtype, h), bf = load_any(a.f_bias, a.bias_dtype, h);
     const float inv_cap = 1.0f / a.cap;
     const float* Kp = a.k + (long)h * D;
@@ -121,32 +124,41 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
             const int tt = idx / cols, c = min(idx - tt * cols, V - 1 - col0);
             vr[e] = __ldg(Vp + (long)(c0 + tt) * a.ldv + c);
         }
-        const float* g = a.gates + (long)(c0 + min((int)threadIdx.x, nt - 1)) * a.ldg;
+    };
+    // The gate warp, a chunk ahead of the others: a lane a token works out the two gates, the chain of maxima runs over
+    // shuffles, and a lane a token takes the three exponentials.
+    auto gates_of = [&](int c0, int nt, int buf) {
+        const int lane = threadIdx.x - ML_THREADS;
+        const float* g = a.gates + (long)(c0 + min(lane, nt - 1)) * a.ldg;
         gir = __ldg(g + h);
         gfr = __ldg(g + H + h);
+        const float gi = a.cap * tanhf((gir + bi) * inv_cap);
+        const float gf = logsigmoid_f(a.cap * tanhf((gfr + bf) * inv_cap));
+        float m = m_run, m_before = 0.f, m_after = 0.f;
+        for (int tt = 0; tt < nt; ++tt) {
+            const float f = __shfl_sync(0xffffffffu, gf, tt), i = __shfl_sync(0xffffffffu, gi, tt);
+            const float mn = fmaxf(f + m, i);
+            if (lane == tt) { m_before = m; m_after = mn; }
+            m = mn;
+        }
+        m_run = m;
+        if (lane < nt) {
+            keep_s[buf][lane] = expf(gf + m_before - m_after);
+            take_s[buf][lane] = expf(gi - m_after);
+            floor_s[buf][lane] = expf(-m_after);
+        }
     };
-    fetch(r0, min(CH, r1 - r0));
-    for (int c0 = r0; c0 < r1; c0 += CH) {
+    if (worker) fetch(r0, min(CH, r1 - r0));
+    else gates_of(r0, min(CH, r1 - r0), 0);
+    for (int c0 = r0, buf = 0; c0 < r1; c0 += CH, buf ^= 1) {
         const int nt = min(CH, r1 - c0);
-        __syncthreads();      // the chunk before is done with the staged rows
-        if (threadIdx.x < 32) {
-            // the chunk's gates, the chain of maxima and the three exponentials of every token, by the first warp
-            const int lane = threadIdx.x;
-            const float gi = a.cap * tanhf((gir + bi) * inv_cap);
-            const float gf = logsigmoid_f(a.cap * tanhf((gfr + bf) * inv_cap));
-            float m = m_run, m_before = 0.f, m_after = 0.f;
-            for (int tt = 0; tt < nt; ++tt) {
-                const float f = __shfl_sync(0xffffffffu, gf, tt), i = __shfl_sync(0xffffffffu, gi, tt);
-                const float mn = fmaxf(f + m, i);
-                if (lane == tt) { m_before = m; m_after = mn; }
-                m = mn;
-            }
-            m_run = m;
-            if (lane < nt) {
-                keep_s[lane] = expf(gf + m_before - m_after);
-                take_s[lane] = expf(gi - m_after);
-                floor_s[lane] = expf(-m_after);
-            }
+        __syncthreads();      // the chunk before is done with the staged rows; this chunk's gates are in place
+        if (!worker) {
+            // (the other warps stage and work on this chunk meanwhile; the buffer written now was last read in the
+            // chunk before this one)
+            __syncthreads();
+            if (c0 + CH < r1) gates_of(c0 + CH, min(CH, r1 - c0 - CH), buf ^ 1);
+            continue;
         }
         if (PRE) {
             const int i = threadIdx.x;
@@ -186,7 +198,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
 #pragma unroll 1
         for (int tt = 0; tt < nt; ++tt) {
             {
-                const float keep = keep_s[tt], take = take_s[tt], tv = take * v_s[tt][cl];
+                const float keep = keep_s[buf][tt], take = take_s[buf][tt], tv = take * v_s[tt][cl];
                 // (four partial sums a dot product: the chain of dependent additions is a quarter as long)
                 float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f, d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
@@ -222,7 +234,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
 #pragma unroll
             for (int tt = 0; tt < CH; ++tt)
                 if (tt < nt)
-                    a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = num[tt] / (fmaxf(fabsf(den[tt]), floor_s[tt]) + 1e-6f);
+                    a.out[(long)(c0 + tt) * a.ldo + (long)h * V + col] = num[tt] / (fmaxf(fabsf(den[tt]), floor_s[buf][tt]) + 1e-6f);
         }
     }
     fx_pdl_trigger();
@@ -233,14 +245,14 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(const MlstmArgs 
             if (row < D) sp[row] = S[i];
         }
     }
-    if (cl == 0) {
+    if (worker && cl == 0) {
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             const int row = (i >> 2) * 4 * R + part * 4 + (i & 3);
             if (row < D) np[row] = N[i];
         }
     }
-    if (threadIdx.x == 0) a.m[copy] = m_run;
+    if (threadIdx.x == ML_THREADS) a.m[copy] = m_run;
 }
 
 // rows a lane holds: a multiple of four
@@ -287,9 +299,9 @@ extern "C" int fx_mlstm_scan(const float* q, long ldq, const float* k, long ldk,
     const bool early = n_tokens < 8 * n_entries;
 #define FX_GO(RPL)                                                                                                    \
     do {                                                                                                              \
-        if (pre == 1) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 1>, grid, ML_THREADS, 0, s, a);                  \
-        else if (pre == 2) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 2>, grid, ML_THREADS, 0, s, a);             \
-        else fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 0>, grid, ML_THREADS, 0, s, a);                           \
+        if (pre == 1) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 1>, grid, ML_BLOCK, 0, s, a);                    \
+        else if (pre == 2) fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 2>, grid, ML_BLOCK, 0, s, a);               \
+        else fx_launch_pdl_if(early, mlstm_scan_kernel<RPL, 0>, grid, ML_BLOCK, 0, s, a);                             \
     } while (0)
     switch (rpl) {
         case 4: FX_GO(4); break;
