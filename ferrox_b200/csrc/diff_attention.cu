@@ -22,6 +22,7 @@
 namespace {
 
 constexpr int MAX_TAPS = 16;
+constexpr int RUN_MAX = 16;      // tokens a block of the prompt form takes
 
 template <typename T>
 __global__ void __launch_bounds__(128) conv_rotary_store_kernel(
@@ -95,6 +96,99 @@ __global__ void __launch_bounds__(128) conv_rotary_store_kernel(
     }
 }
 
+// The same for a prompt's portion: one block a (run of tokens, head).  The run's projected rows of the head, with the
+// taps - 1 rows before them, are staged once in shared memory (32-bit) beside the head's taps, so that every input
+// is read from memory once; the (token, element) pairs of the run are then shared out over the threads.  Inputs
+// before an entry's first row of the step come from the slot's tail as ever.
+template <typename T>
+__global__ void __launch_bounds__(128) conv_rotary_store_run_kernel(
+    const T* __restrict__ proj, long ldp, const void* __restrict__ w, int w_dtype, int taps, const float* __restrict__ tail,
+    const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+    const float* __restrict__ cos_sin, int rot_dims, int pairing, T* __restrict__ q_out, long ldq,
+    T* __restrict__ k_pages, T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+    int page_size, int n_tokens, int run, int n_q_heads, int n_k_heads, int head_dim, int n_v_heads, int value_dim,
+    int write_cache, int* __restrict__ status)
+{
+    extern __shared__ float run_s[];      // [run + taps - 1][width] rows, then [width][taps] weights
+    fx_pdl_wait();
+    const int head = blockIdx.y;
+    const int t0 = blockIdx.x * run, t1 = min(n_tokens, t0 + run);
+    const int first = max(0, t0 - (taps - 1));      // the first staged row
+    const int qk = (n_q_heads + n_k_heads) * head_dim, C = qk + n_v_heads * value_dim;
+    const bool is_q = head < n_q_heads, is_v = head >= n_q_heads + n_k_heads;
+    const int width = is_v ? value_dim : head_dim;
+    const int c0 = is_v ? qk + (head - n_q_heads - n_k_heads) * value_dim : head * head_dim;    // the head's first channel
+    float* w_s = run_s + (long)(run + taps - 1) * width;
+    for (int idx = threadIdx.x; idx < (t1 - first) * width; idx += blockDim.x) {
+        const int r = idx / width, i = idx - r * width;
+        run_s[idx] = to_f32(proj[(long)(first + r) * ldp + c0 + i]);
+    }
+    for (int idx = threadIdx.x; idx < width * taps; idx += blockDim.x) w_s[idx] = load_any(w, w_dtype, (long)c0 * taps + idx);
+    // what the run's tokens need beside their rows, worked out once a token: how many rows before it belong to the same
+    // entry (at most taps - 1 matter), its slot's tail, and where the head's elements go
+    __shared__ int own_s[RUN_MAX];
+    __shared__ const float* tl_s[RUN_MAX];
+    __shared__ T* dst_s[RUN_MAX];
+    if (threadIdx.x < t1 - t0) {
+        const int t = t0 + threadIdx.x;
+        const int b = token_seq[t];
+        const int slot = seq_slot[b];
+        int own = 0;
+        while (own < taps - 1 && t - own - 1 >= 0 && token_seq[t - own - 1] == b) ++own;
+        own_s[threadIdx.x] = own;
+        tl_s[threadIdx.x] = tail + (long)slot * (taps - 1) * C + c0;
+        T* dst = nullptr;
+        if (is_q) {
+            dst = q_out + (long)t * ldq + (long)head * head_dim;
+        } else if (write_cache) {
+            const int pos = positions[t];
+            const int page = block_table[(long)slot * table_width + pos / page_size];
+            if (page < 0) { if (status) atomicExch(status, 2); }
+            else if (is_v) dst = v_pages + (((long)page * n_v_heads + (head - n_q_heads - n_k_heads)) * page_size + (pos % page_size)) * value_dim;
+            else dst = k_pages + (((long)page * n_k_heads + (head - n_q_heads)) * page_size + (pos % page_size)) * head_dim;
+        }
+        dst_s[threadIdx.x] = dst;
+    }
+    __syncthreads();
+    const int rot = (is_v || !cos_sin) ? 0 : rot_dims, half = rot >> 1;
+    for (int idx = threadIdx.x; idx < (t1 - t0) * width; idx += blockDim.x) {
+        const int tt = idx / width, i = idx - tt * width, t = t0 + tt;
+        int i1 = -1, p = 0;      // the partner of a rotated element and the pair's index
+        if (i < rot) {
+            if (pairing ? (i & 1) : (i >= half)) continue;      // (its partner does both)
+            p = pairing ? i >> 1 : i;
+            i1 = pairing ? i + 1 : i + half;
+        }
+        T* dst = dst_s[tt];
+        if (!dst) continue;
+        const int own = own_s[tt];
+        const float* tl = tl_s[tt];
+        float a = 0.f, bb = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int back = taps - 1 - j;      // this tap's input lies `back` tokens before t
+            float va, vb = 0.f;
+            if (back <= own) {
+                const float* r = run_s + (long)(t - back - first) * width;
+                va = r[i];
+                if (i1 >= 0) vb = r[i1];
+            } else {
+                const float* r = tl + (long)(taps - 1 - (back - own)) * C;
+                va = r[i];
+                if (i1 >= 0) vb = r[i1];
+            }
+            a = fmaf(w_s[i * taps + j], va, a);
+            if (i1 >= 0) bb = fmaf(w_s[i1 * taps + j], vb, bb);
+        }
+        if (i1 >= 0) {
+            const float* cs = cos_sin + ((long)t * (rot_dims >> 1) + p) * 2;
+            dst[i] = from_f32<T>(a * cs[0] - bb * cs[1]);
+            dst[i1] = from_f32<T>(bb * cs[0] + a * cs[1]);
+        } else {
+            dst[i] = from_f32<T>(a);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) diff_combine_kernel(const T* __restrict__ attn, long lda, T* __restrict__ out,
                                                            long ldo, int n_tokens, int n_heads, int group, int V,
@@ -135,8 +229,27 @@ extern "C" int fx_conv_rotary_store(const void* proj, int dtype, long ldp, const
         n_v_heads <= 0 || proj == q_out)
         return FX_ERR_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_tokens, n_q_heads + n_k_heads + n_v_heads);
     const int widest = head_dim > value_dim ? head_dim : value_dim;
+    if (!update_tail && n_tokens >= 64) {
+        // a prompt's portion: runs of tokens whose rows a block stages once (as many as 40 KB of shared memory hold)
+        int run = (int)(40 * 1024 / 4 / widest) - 2 * taps;
+        run = run > RUN_MAX ? RUN_MAX : run;
+        if (run >= 4) {
+            const dim3 rgrid((unsigned)fx_cdiv(n_tokens, run), n_q_heads + n_k_heads + n_v_heads);
+            const size_t smem = ((size_t)(run + taps - 1) * widest + (size_t)widest * taps) * sizeof(float);
+#define FX_RUN(T)                                                                                                     \
+    fx_launch_pdl(conv_rotary_store_run_kernel<T>, rgrid, 128, smem, s, (const T*)proj, ldp, w, w_dtype, taps,         \
+                  (const float*)tail, positions, token_seq, seq_slot, cos_sin, rot_dims, pairing, (T*)q_out, ldq,     \
+                  (T*)k_pages, (T*)v_pages, block_table, table_width, page_size, n_tokens, run, n_q_heads, n_k_heads, \
+                  head_dim, n_v_heads, value_dim, write_cache, status)
+            if (dtype == FX_F32) FX_RUN(float);
+            else if (dtype == FX_BF16) FX_RUN(bf16);
+            else return FX_ERR_DTYPE;
+#undef FX_RUN
+            return fx_launch_status();
+        }
+    }
+    const dim3 grid(n_tokens, n_q_heads + n_k_heads + n_v_heads);
     const int nt = widest <= 32 ? 32 : widest <= 64 ? 64 : 128;
 #define FX_GO(T)                                                                                                      \
     fx_launch_pdl(conv_rotary_store_kernel<T>, grid, nt, 0, s, (const T*)proj, ldp, w, w_dtype, taps, tail,           \

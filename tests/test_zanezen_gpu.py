@@ -120,9 +120,12 @@ def diff_mixer(H, G, D, V, scale, diff, taps, rotary, softcap):
 
 
 SCALED = {"dims": 16, "base": 500.0, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}
+# beside the cuts of the other mixers' tests: portions of two requests in one step that are long enough for the
+# prompt form of the convolution kernel, the second request beginning in the middle of a run of tokens
+DIFF_CUTS = dict(CUTS, **{"large portions": [(70, 30), (50, 7), (30, 0)]})
 
 
-@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("cut", list(DIFF_CUTS))
 @pytest.mark.parametrize("H,G,D,V,taps,rotary,softcap,page", [
     (4, 2, 32, 48, 4, SCALED, 20.0, 4), (3, 3, 20, 12, 3, {"dims": 8, "base": 1000.0}, 5.0, 8), (6, 1, 24, 40, None, None, None, 16),
     (8, 1, 64, 128, 5, {"dims": 32, "base": 20000.0, "scaling": {"factor": 2.0, "original": 256, "fast": 32.0, "slow": 1.0}}, 30.0, 64),
@@ -144,10 +147,10 @@ def test_differential_attention_alone(dtype, H, G, D, V, taps, rotary, softcap, 
         with pz.rounded_to(torch.bfloat16):     # the difference of two rounded maps, normed: rounding is amplified
             tol = max(tol, 4 * max(rel(pz.differential_attention(m, floats(w), "m.", x, 1e-5), b) for x, b in zip(xs, want)))
     h = MixerHarness(part, rt, hidden, page_size=page, n_pages=256 // page + 8)
-    got = run_in_cuts(h, xs, CUTS[cut])
+    got = run_in_cuts(h, xs, DIFF_CUTS[cut])
     for a, b in zip(got, want):
         assert rel(a, b) < tol
-    got = run_in_cuts(h, xs[::-1], CUTS[cut])
+    got = run_in_cuts(h, xs[::-1], [(b, a) for a, b in DIFF_CUTS[cut]] if cut == "large portions" else DIFF_CUTS[cut])
     for a, b in zip(got, want[::-1]):
         assert rel(a, b) < tol
 
