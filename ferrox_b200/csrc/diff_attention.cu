@@ -11,7 +11,9 @@
 // any factor on cos and sin; pairs (i, i + rot_dims / 2) or neighbours), q goes to q_out and k and v to the pages
 // (k [pages, k heads, page, head_dim], v [pages, v heads, page, value_dim]).  Sums and rotation are 32-bit; the
 // element type is that of the projected rows.  A step of one token a request (update_tail) also moves the tail on;
-// other steps call fx_conv_tail_update on the projected rows afterwards.
+// other steps call fx_conv_tail_update on the projected rows afterwards.  A prompt's portion (64 tokens or more)
+// goes in runs of up to 16 tokens a block instead, whose rows are staged once in shared memory
+// (conv_rotary_store_run_kernel).
 //
 // fx_diff_combine, one warp a (token, head).  The attention ran over twice as many query heads as the mixer has:
 // for the heads hg = 0 .. group - 1 of kv head g, map j of head g * group + hg is row (2 g + j) * group + hg of the
